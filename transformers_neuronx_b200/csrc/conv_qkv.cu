@@ -377,3 +377,18 @@ TNX_EXPORT int tnx_conv_qkv_prep(const void* proj, int ld, int col0, const float
                          n_requests, update_state, q_norm, k_norm, eps, inv_freq, rot_dims, interleaved, magnitude, q_out,
                          k_out, v_out, N, H, G, dk, dv, D, stream);
 }
+
+// The state kernel alone, for another mixer whose own kernel does the convolution: the state [slots, keep, channels] of
+// every request with more than one row becomes its last `keep` projected values (columns col0 .. col0 + channels of proj).
+TNX_EXPORT int tnx_conv_state_update(const void* proj, int ld, int col0, void* state, int keep, int channels,
+                                     const int* q_start, const int* q_len, const int* state_slots, int n_requests,
+                                     int is_h16, cudaStream_t stream) {
+    if (n_requests <= 0 || keep <= 0) return 0;
+    if (channels <= 0 || !proj || !state) return TNX_ERR_BAD_ARG;
+    const dim3 grid((channels + 127) / 128, n_requests);
+    if (is_h16)
+        return tnx_launch_in_order(conv_state_update_kernel<h16>, grid, dim3(128), 0, stream, (const h16*)proj, ld, col0,
+                                   (h16*)state, keep, channels, q_start, q_len, state_slots);
+    return tnx_launch_in_order(conv_state_update_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, ld, col0,
+                               (float*)state, keep, channels, q_start, q_len, state_slots);
+}

@@ -1,0 +1,206 @@
+// A recurrence with an error-correcting write ("delta rule") and a decay per head and key channel.  Per head, with
+// q_t, k_t of k_dim numbers, v_t of v_dim numbers and a state S of k_dim x v_dim (32-bit, kept per request):
+//     S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+// so the read-out sees the current token's write.  Query/key heads may be shared by groups of heads (G of them for H
+// heads: head h uses q/k head h / (H / G)).
+//
+// tnx_delta_prep, one thread block per token: from the projections' output (queries, keys and values side by side
+//   from column col0 on: G*dk, G*dk, H*dv channels)
+//     y_t[c] = act(sum_j w[j, c] u_(t - taps + 1 + j)[c])        the short causal convolution (zeros before position 0;
+//                                                                 the past comes from this step's rows or from the
+//                                                                 request's state [slots, taps - 1, channels])
+//     q, k per head: y / sqrt(sum(y^2) + unit_eps), q times q_scale;  v = y
+//     beta[h] = sigmoid(proj[b_off + h]);   g[h, i] = exp(-exp(a_log[h]) * softplus(a[h * dk + i] + dt_bias[h * dk + i]))
+//   Everything after the loads is 32-bit and stays 32-bit: q, k, v, beta and g are written as floats.  A request with
+//   one row shifts its convolution state here; requests with several rows are brought up to date by the convolution
+//   library's state kernel afterwards.
+// tnx_delta_scan: a thread block owns C columns (value dims) of one head of one request and walks the request's tokens
+//   of this step in order, the state's columns in registers: a column's k_dim rows are spread over R adjacent lanes,
+//   which add their partial sums of S^T k, S^T q and q.k with shuffles (one round for all three: o = (gS)^T q + (q.k) u).
+//   The state is stored [slot, head, v_dim, k_dim] (a column's rows side by side).
+#include "common.cuh"
+
+namespace {
+
+constexpr int PREP_MAX_TAPS = 8;
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(const T* __restrict__ proj, int ld, int col0, int b_off, const float* __restrict__ a, int a_ld,
+                  const float* __restrict__ conv_w, int taps, T* state, const int* __restrict__ token_request,
+                  const int* __restrict__ positions, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                  const int* __restrict__ state_slots, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                  float unit_eps, float q_scale, int act, float* __restrict__ q_out, float* __restrict__ k_out,
+                  float* __restrict__ v_out, float* __restrict__ beta_out, float* __restrict__ g_out, int H, int G, int dk,
+                  int dv) {
+    extern __shared__ float y[];                      // the token's convolved channels
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int req = token_request[n];
+    if (req < 0) return;                              // a padded row of a captured step
+    const int pos = positions[n], idx = n - q_start[req], slot = state_slots[req];
+    const bool alone = q_len[req] == 1;
+    const int keep = taps - 1, nqk = 2 * G * dk, C = nqk + H * dv;
+    const T* row = proj + (size_t)n * ld + col0;
+    T* st = (keep > 0 && slot >= 0) ? state + (size_t)slot * keep * C : nullptr;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float past[PREP_MAX_TAPS];                    // past[b]: the projected value b positions back
+        past[0] = to_float(row[c]);
+        for (int b = 1; b < taps; ++b) {
+            float v = 0.f;
+            if (pos - b >= 0) {
+                if (idx - b >= 0) v = to_float(row[c - (ptrdiff_t)b * ld]);
+                else if (st) v = to_float(st[(size_t)(keep + idx - b) * C + c]);
+            }
+            past[b] = v;
+        }
+        float s = 0.f;
+        for (int j = 0; j < taps; ++j) s = fmaf(conv_w[(size_t)j * C + c], past[taps - 1 - j], s);
+        if (alone && st)                              // oldest first: what was one back is now two back
+            for (int q = 0; q < keep; ++q) st[(size_t)q * C + c] = from_float<T>(past[keep - 1 - q]);
+        y[c] = apply_activation(s, act);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int u = warp; u < 2 * G; u += warps) {       // unit vectors: the heads of q, then those of k
+        const float* src = y + u * dk;
+        float ss = 0.f;
+        for (int i = lane; i < dk; i += 32) ss = fmaf(src[i], src[i], ss);
+        const float rinv = (u < G ? q_scale : 1.f) / sqrtf(warp_sum(ss) + unit_eps);
+        float* dst = (u < G ? q_out + (size_t)n * G * dk + u * dk : k_out + (size_t)n * G * dk + (u - G) * dk);
+        for (int i = lane; i < dk; i += 32) dst[i] = src[i] * rinv;
+    }
+    for (int c = threadIdx.x; c < H * dv; c += blockDim.x) v_out[(size_t)n * H * dv + c] = y[nqk + c];
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        beta_out[(size_t)n * H + h] = 1.f / (1.f + expf(-to_float(proj[(size_t)n * ld + b_off + h])));
+    for (int c = threadIdx.x; c < H * dk; c += blockDim.x) {
+        const float rate = expf(a_log[c / dk]);
+        g_out[(size_t)n * H * dk + c] = expf(-rate * softplus_f(a[(size_t)n * a_ld + c] + dt_bias[c]));
+    }
+}
+
+// tokens whose inputs are staged in shared memory at a time (fewer for the longest keys: 48 KB of static shared memory)
+__host__ __device__ constexpr int scan_stage(int dkp) { return dkp > 128 ? 8 : 16; }
+
+// KPT: rows of a column one thread keeps; R: lanes a column's rows are spread over (KPT * R >= k_dim); a block of 128
+// threads owns 128 / R columns.
+template <int KPT, int R>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                  const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state,
+                  const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ state_slots,
+                  float* __restrict__ out, int H, int G, int dk, int dv) {
+    constexpr int DKP = KPT * R, C = 128 / R, SCAN_STAGE = scan_stage(KPT * R);
+    __shared__ float qs[SCAN_STAGE][DKP], ks[SCAN_STAGE][DKP], gs[SCAN_STAGE][DKP], vs[SCAN_STAGE][C], bs[SCAN_STAGE];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int req = blockIdx.z, h = blockIdx.y;
+    const int len = q_len[req];
+    if (len <= 0) return;                             // a padded request of a captured batch
+    const int slot = state_slots[req];
+    if (slot < 0) return;
+    const int t_first = q_start[req], kvh = h / (H / G);
+    const int jl = threadIdx.x / R, r = threadIdx.x % R;
+    const int j = blockIdx.x * C + jl;
+    const bool col = j < dv;
+    float* st = state + (((size_t)slot * H + h) * dv + (col ? j : 0)) * dk;
+    float S[KPT];
+#pragma unroll
+    for (int m = 0; m < KPT; ++m) S[m] = (col && r + R * m < dk) ? st[r + R * m] : 0.f;
+    for (int t0 = 0; t0 < len; t0 += SCAN_STAGE) {
+        const int nt = min(SCAN_STAGE, len - t0);
+        __syncthreads();                              // the stage before is no longer read
+        for (int e = threadIdx.x; e < nt * DKP; e += 128) {
+            const int tt = e / DKP, i = e % DKP;
+            const size_t t = (size_t)(t_first + t0 + tt);
+            const bool in = i < dk;
+            qs[tt][i] = in ? q[(t * G + kvh) * dk + i] : 0.f;
+            ks[tt][i] = in ? k[(t * G + kvh) * dk + i] : 0.f;
+            gs[tt][i] = in ? g[(t * H + h) * dk + i] : 0.f;
+        }
+        for (int e = threadIdx.x; e < nt * C; e += 128) {
+            const int tt = e / C, c = blockIdx.x * C + e % C;
+            vs[tt][e % C] = c < dv ? v[((size_t)(t_first + t0 + tt) * H + h) * dv + c] : 0.f;
+        }
+        if (threadIdx.x < nt) bs[threadIdx.x] = beta[(size_t)(t_first + t0 + threadIdx.x) * H + h];
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            float sk = 0.f, sq = 0.f, qk = 0.f;
+#pragma unroll
+            for (int m = 0; m < KPT; ++m) {
+                const int i = r + R * m;
+                const float kk = ks[tt][i], qq = qs[tt][i];
+                S[m] *= gs[tt][i];
+                sk = fmaf(kk, S[m], sk);
+                sq = fmaf(qq, S[m], sq);
+                qk = fmaf(qq, kk, qk);
+            }
+#pragma unroll
+            for (int o = R >> 1; o > 0; o >>= 1) {    // the R lanes of a column are neighbours in one warp
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                qk += __shfl_xor_sync(0xffffffffu, qk, o);
+            }
+            const float u = bs[tt] * (vs[tt][jl] - sk);
+#pragma unroll
+            for (int m = 0; m < KPT; ++m) S[m] = fmaf(ks[tt][r + R * m], u, S[m]);
+            if (r == 0 && col) out[((size_t)(t_first + t0 + tt) * H + h) * dv + j] = fmaf(qk, u, sq);
+        }
+    }
+    if (col) {
+#pragma unroll
+        for (int m = 0; m < KPT; ++m)
+            if (r + R * m < dk) st[r + R * m] = S[m];
+    }
+}
+
+}  // namespace
+
+TNX_EXPORT int tnx_delta_prep(const void* proj, int ld, int col0, int b_off, const float* a, int a_ld, const float* conv_w,
+                              int taps, void* state, const int* token_request, const int* positions, const int* q_start,
+                              const int* q_len, const int* state_slots, const float* a_log, const float* dt_bias,
+                              float unit_eps, float q_scale, int act, float* q_out, float* k_out, float* v_out,
+                              float* beta_out, float* g_out, int n_tokens, int H, int G, int dk, int dv, int is_h16,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1 || taps > PREP_MAX_TAPS || !conv_w ||
+        (taps > 1 && !state) || act < 0 || act >= TNX_ACT_COUNT)
+        return TNX_ERR_BAD_ARG;
+    const size_t smem = (size_t)(2 * G * dk + H * dv) * sizeof(float);
+    if (smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
+#define DPREP(T)                                                                                                        \
+    do {                                                                                                                \
+        if (smem > 48 * 1024)                                                                                           \
+            cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+        return tnx_launch_in_order(delta_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, stream, (const T*)proj, ld,   \
+                                   col0, b_off, a, a_ld, conv_w, taps, (T*)state, token_request, positions, q_start,    \
+                                   q_len, state_slots, a_log, dt_bias, unit_eps, q_scale, act, q_out, k_out, v_out,      \
+                                   beta_out, g_out, H, G, dk, dv);                                                      \
+    } while (0)
+    if (is_h16) DPREP(h16);
+    DPREP(float);
+#undef DPREP
+}
+
+TNX_EXPORT int tnx_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* g,
+                              float* state, const int* q_start, const int* q_len, const int* state_slots, float* out,
+                              int n_requests, int H, int G, int dk, int dv, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0) return TNX_ERR_BAD_ARG;
+#define DSCAN(KPT, R)                                                                                                   \
+    do {                                                                                                                \
+        const int C = 128 / (R);                                                                                        \
+        return tnx_launch_in_order(delta_scan_kernel<KPT, R>, dim3((dv + C - 1) / C, H, n_requests), dim3(128), 0,      \
+                                   stream, q, k, v, beta, g, state, q_start, q_len, state_slots, out, H, G, dk, dv);    \
+    } while (0)
+    if (dk <= 16) DSCAN(4, 4);
+    if (dk <= 32) DSCAN(4, 8);
+    if (dk <= 64) DSCAN(8, 8);
+    if (dk <= 128) DSCAN(8, 16);
+    if (dk <= 256) DSCAN(16, 16);
+    return TNX_ERR_UNSUPPORTED;
+#undef DSCAN
+}

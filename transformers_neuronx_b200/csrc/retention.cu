@@ -15,8 +15,8 @@
 //   contiguous piece.  A step of one token per request streams the state through once; a portion of a prompt
 //   keeps it in registers for all its tokens.  Queries and keys of a few tokens at a time are staged in shared memory.
 // tnx_headwise_gated_rms_norm: o of each (token, head) divided by its root mean square (eps inside the root,
-//   an optional weight over the head's dims), multiplied by silu(gate) and by out_scale, written in the
-//   activation type.
+//   an optional weight over the head's dims), multiplied by act(gate) (silu here; the activation is a parameter) and
+//   by out_scale, written in the activation type.
 #include "common.cuh"
 
 namespace {
@@ -464,7 +464,7 @@ template <typename T>
 __global__ void headwise_gated_rms_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_ld,
                                                const int* __restrict__ token_request, const float* __restrict__ w,
                                                float eps, float out_scale, T* __restrict__ out, int out_ld,
-                                               int n_tokens, int H, int dv) {
+                                               int n_tokens, int H, int dv, int gate_act) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -495,7 +495,7 @@ __global__ void headwise_gated_rms_norm_kernel(const float* __restrict__ o, cons
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 if (w) y[e] *= w[c + e];
-                if (g) { const float z = to_float(g[c + e]); y[e] *= z / (1.f + expf(-z)); }
+                if (g) y[e] *= apply_activation(to_float(g[c + e]), gate_act);
                 dst[c + e] = from_float<T>(y[e] * out_scale);
             }
         }
@@ -508,7 +508,7 @@ __global__ void headwise_gated_rms_norm_kernel(const float* __restrict__ o, cons
     for (int c = lane; c < dv; c += 32) {
         float y = src[c] * rinv;
         if (w) y *= w[c];
-        if (g) { const float z = to_float(g[c]); y *= z / (1.f + expf(-z)); }
+        if (g) y *= apply_activation(to_float(g[c]), gate_act);
         dst[c] = from_float<T>(y * out_scale);
     }
 }
@@ -614,19 +614,19 @@ TNX_EXPORT int tnx_retention_scan(const float* qr, const float* kr, const void* 
 
 TNX_EXPORT int tnx_headwise_gated_rms_norm(const float* o, const void* gate, int gate_ld, const int* token_request,
                                            const float* w, float eps, float out_scale, void* out, int out_ld,
-                                           int n_tokens, int H, int dv, int is_h16, cudaStream_t stream) {
+                                           int n_tokens, int H, int dv, int gate_act, int is_h16, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (H <= 0 || dv <= 0 || out_ld < H * dv) return TNX_ERR_BAD_ARG;
+    if (H <= 0 || dv <= 0 || out_ld < H * dv || gate_act < 0 || gate_act >= TNX_ACT_COUNT) return TNX_ERR_BAD_ARG;
     const int warps = 4;
     const long long pairs = (long long)n_tokens * H;
     const int blocks = (int)((pairs + warps - 1) / warps);
     if (is_h16)
         return tnx_launch_in_order(headwise_gated_rms_norm_kernel<h16>, dim3(blocks), dim3(warps * 32), 0, stream, o,
                                    (const h16*)gate, gate_ld, token_request, w, eps, out_scale, (h16*)out, out_ld, n_tokens,
-                                   H, dv);
+                                   H, dv, gate_act);
     return tnx_launch_in_order(headwise_gated_rms_norm_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, o,
                                (const float*)gate, gate_ld, token_request, w, eps, out_scale, (float*)out, out_ld, n_tokens,
-                               H, dv);
+                               H, dv, gate_act);
 }
 
 // One token per request: rotation, state update, output, head-wise norm, gate and scale in one kernel.  Returns

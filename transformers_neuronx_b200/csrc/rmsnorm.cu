@@ -47,10 +47,13 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, float x_scale, cons
 
 // The norm on a sublayer's output only:  out = x + add_scale * (delta / sqrt(mean(delta^2) + eps) * (w + w_offset)).
 // x is the 32-bit residual stream (out_f32 may be x itself), delta what the sublayer produced.
+// then_norm: out_act receives a further RMS norm of the new row, out / sqrt(mean(out^2) + then_eps) * (w_then + then_offset),
+// which is the input of the sublayer that follows (a norm before and after every sublayer); otherwise the row's copy.
 template <typename TA, bool VEC>
 __global__ void rms_norm_add_kernel(const float* x, float add_scale, const float* __restrict__ delta,
                                     const float* __restrict__ w, float w_offset, float eps, float* out_f32,
-                                    TA* __restrict__ out_act, int H) {
+                                    TA* __restrict__ out_act, int H, int then_norm, const float* __restrict__ w_then,
+                                    float then_offset, float then_eps) {
     extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -73,17 +76,27 @@ __global__ void rms_norm_add_kernel(const float* x, float add_scale, const float
     }
     const float ms = block_sum(s, scratch) / (float)H;
     const float rinv = 1.0f / sqrtf(ms + eps);
+    float s2 = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float y = row[c] * rinv;
         if (w) y *= (w[c] + w_offset);
         y = fmaf(add_scale, y, x[src + c]);
         if (out_f32) out_f32[src + c] = y;
-        if (out_act) out_act[src + c] = from_float<TA>(y);
+        if (then_norm) { row[c] = y; s2 += y * y; }
+        else if (out_act) out_act[src + c] = from_float<TA>(y);
+    }
+    if (!then_norm || !out_act) return;
+    const float rinv2 = 1.0f / sqrtf(block_sum(s2, scratch) / (float)H + then_eps);     // each thread reads back its own columns
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float y = row[c] * rinv2;
+        if (w_then) y *= (w_then[c] + then_offset);
+        out_act[src + c] = from_float<TA>(y);
     }
 }
 
 TNX_EXPORT int tnx_rms_norm_add(const float* x, float add_scale, const float* delta, const float* w, float w_offset,
                                 float eps, float* out_f32, void* out_act, int n_rows, int H, int act_h16,
+                                int then_norm, const float* w_then, float then_offset, float then_eps,
                                 cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const size_t smem = (size_t)H * sizeof(float);
@@ -95,7 +108,8 @@ TNX_EXPORT int tnx_rms_norm_add(const float* x, float add_scale, const float* de
         if (smem + 1024 > 48 * 1024)                                                                                   \
             cudaFuncSetAttribute(rms_norm_add_kernel<TA, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         return tnx_launch_ex(1, rms_norm_add_kernel<TA, V>, dim3(n_rows), dim3(threads), smem, stream, x, add_scale,   \
-                             delta, w, w_offset, eps, out_f32, (TA*)out_act, H);                                       \
+                             delta, w, w_offset, eps, out_f32, (TA*)out_act, H, then_norm, w_then, then_offset,        \
+                             then_eps);                                                                                \
     } while (0)
     if (act_h16) { if (vec) RMS_LAUNCH(h16, true); else RMS_LAUNCH(h16, false); }
     if (vec) RMS_LAUNCH(float, true); else RMS_LAUNCH(float, false);

@@ -51,6 +51,8 @@ SOURCES: Dict[str, str] = {
     "conv_qkv": "conv_qkv.cu",
     "moe": "moe.cu",
     "moe_grouped": "moe_grouped.cu",
+    "latent_attention": "latent_attention.cu",
+    "delta_rule": "delta_rule.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -816,9 +816,10 @@ def rms_norm(x, weight, eps, out_f32=None, out_act=None, rows=None, x_scale=1.0,
                             c_int(_is_h16(out_act) if out_act is not None else 0), _stream()), "rms_norm")
 
 
-def rms_norm_add(x, add_scale, delta, weight, eps, out_f32=None, out_act=None, weight_offset=0.0):
+def rms_norm_add(x, add_scale, delta, weight, eps, out_f32=None, out_act=None, weight_offset=0.0, then=None):
     """x + add_scale * (delta / rms(delta) * (weight + weight_offset)): the norm on a sublayer's output alone, added to
-    the 32-bit stream x.  out_f32 may be x itself."""
+    the 32-bit stream x.  out_f32 may be x itself.  then = (weight or None, weight_offset, eps): out_act receives that
+    further RMS norm of the new row (the input of the sublayer that follows) instead of the row's copy."""
     lib = _lib("rmsnorm", out_act)
     _need(x, "x", torch.float32, 2)
     _need(delta, "delta", torch.float32, 2)
@@ -831,9 +832,12 @@ def rms_norm_add(x, add_scale, delta, weight, eps, out_f32=None, out_act=None, w
             _need(t, nm, torch.float32 if nm == "out_f32" else _FLOATS, 2)
             if tuple(t.shape) != (N, H):
                 raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{N}, {H}]")
+    w_then, off_then, eps_then = then if then is not None else (None, 0.0, 0.0)
+    _f32_vec(w_then, "the following norm's weight", H)
     _check(lib.tnx_rms_norm_add(_p(x), c_float(add_scale), _p(delta), _p(weight), c_float(weight_offset), c_float(eps),
                                 _p(out_f32), _p(out_act), c_int(N), c_int(H),
-                                c_int(_is_h16(out_act) if out_act is not None else 0), _stream()), "rms_norm_add")
+                                c_int(_is_h16(out_act) if out_act is not None else 0), c_int(1 if then is not None else 0),
+                                _p(w_then), c_float(off_then), c_float(eps_then), _stream()), "rms_norm_add")
 
 
 def conv_qkv_prep(proj, col0, conv_w, taps, state, ctx, q_norm, k_norm, eps, inv_freq, rot_dims, interleaved, magnitude,
@@ -1150,9 +1154,9 @@ def retention_decode(proj, q_off, k_off, v_off, g_off, positions, inv_freq, rot_
     return True
 
 
-def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out, n_heads, v_dim):
-    """out = o / rms(o over each head's v_dim dims) (* weight) * silu(gate) * out_scale; o 32-bit [N, n_heads * v_dim],
-    gate (optional) and out views in the activation type."""
+def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out, n_heads, v_dim, gate_activation="silu"):
+    """out = o / rms(o over each head's v_dim dims) (* weight) * act(gate) * out_scale; o 32-bit [N, n_heads * v_dim],
+    gate (optional) and out views in the activation type; act: silu unless named otherwise."""
     lib = _lib("retention", gate, out)
     _need(o, "o", torch.float32, 2)
     N = o.shape[0]
@@ -1171,7 +1175,8 @@ def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out,
     _f32_vec(weight, "weight", v_dim)
     _check(lib.tnx_headwise_gated_rms_norm(_p(o), _p(gate), c_int(gate_ld), _p(token_request), _p(weight), c_float(eps),
                                            c_float(out_scale), _p(out), c_int(out_ld), c_int(N), c_int(n_heads),
-                                           c_int(v_dim), c_int(_is_h16(out)), _stream()), "headwise_gated_rms_norm")
+                                           c_int(v_dim), c_int(activation_code(gate_activation)), c_int(_is_h16(out)),
+                                           _stream()), "headwise_gated_rms_norm")
 
 
 def mingru_scan(proj, z_off, x_off, g_off, state, q_start, q_len, state_slots, out, width, out_scale=1.0,
@@ -1213,3 +1218,135 @@ def gated_activation(gate_up, out, activation):
         raise KernelError(f"gate_up must be [{No}, {2 * F}]")
     _check(lib.tnx_gated_activation(_p(gate_up), c_int(ld), _p(out), c_int(out_ld), c_int(N), c_int(F),
                                     c_int(activation_code(activation)), c_int(_is_h16(out)), _stream()), "gated_activation")
+
+
+# ---------------------------------------------------------------------------------------------
+# Attention through low-rank latents; the recurrence with an error-correcting write.
+def latent_prep(proj, col0, token_request, positions, q_norm, kv_norm, eps, inv_freq, interleaved, cq_out, k_out, v_out,
+                q_rank, kv_rank, rot_dim):
+    """From the down projections' output `proj` [N, *] (from column col0 on: q_rank, kv_rank, rot_dim columns): the
+    queries' latent normalised (times q_norm) into cq_out [N, q_rank]; the keys'/values' latent normalised (times
+    kv_norm) into the first kv_rank dims of k_out and v_out [N, D]; the rotated key part turned by position behind it
+    in k_out; the rest of both rows zero."""
+    lib = _lib("latent_attention", proj, cq_out)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    if col0 < 0 or col0 + q_rank + kv_rank + rot_dim > width:
+        raise KernelError("the projection is narrower than its latent columns")
+    _need(cq_out, "cq_out", proj.dtype, 2)
+    _need(k_out, "k_out", proj.dtype, 2)
+    _need(v_out, "v_out", proj.dtype, 2)
+    D = k_out.shape[1]
+    if tuple(cq_out.shape) != (N, q_rank) or tuple(k_out.shape) != (N, D) or tuple(v_out.shape) != (N, D):
+        raise KernelError("cq_out must be [N, q_rank], k_out and v_out [N, D]")
+    _f32_vec(q_norm, "q_norm", q_rank); _f32_vec(kv_norm, "kv_norm", kv_rank)
+    _f32_vec(inv_freq, "inv_freq", rot_dim // 2 if rot_dim else None)
+    _need(token_request, "token_request", torch.int32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    _check(lib.tnx_latent_prep(_p(proj), c_int(ld), c_int(col0), _p(token_request), _p(positions), _p(q_norm), _p(kv_norm),
+                               c_float(eps), _p(inv_freq), c_int(1 if interleaved else 0), _p(cq_out), _p(k_out), _p(v_out),
+                               c_int(N), c_int(q_rank), c_int(kv_rank), c_int(rot_dim if inv_freq is not None else 0),
+                               c_int(D), c_int(_is_h16(proj)), _stream()), "latent_prep")
+
+
+def headwise_product(x, x_head, w, out, out_head, token_request, n_heads, k, n_out, positions=None, inv_freq=None,
+                     rot_dims=0, interleaved=False, pad_to=0, do_product=True):
+    """out[n, h * out_head + c] = sum_i x[n, h * x_head + i] * w[h, i, c] (i < k, c < n_out), 32-bit sums; x, w and out in
+    one type; w [n_heads, k, n_out].  rot_dims > 0: the head's next rot_dims inputs are turned by the token's position
+    into the columns behind n_out, and the head's columns up to pad_to are zeroed.  do_product False: only that."""
+    lib = _lib("latent_attention", x, out)
+    _need(x, "x", _FLOATS, None, contiguous=False)
+    _need(out, "out", x.dtype, None, contiguous=False)
+    N, wx, x_ld = _rows_2d(x, "x")
+    No, wo, out_ld = _rows_2d(out, "out")
+    if No != N or wx < (n_heads - 1) * x_head + k + rot_dims or wo < (n_heads - 1) * out_head + max(n_out, pad_to):
+        raise KernelError("x or out is narrower than its heads")
+    if do_product:
+        _need(w, "w", x.dtype, 3)
+        if tuple(w.shape) != (n_heads, k, n_out):
+            raise KernelError(f"w must be [{n_heads}, {k}, {n_out}]")
+    _need(token_request, "token_request", torch.int32, 1)
+    if rot_dims:
+        _need(positions, "positions", torch.int32, 1)
+        _f32_vec(inv_freq, "inv_freq", rot_dims // 2)
+    _check(lib.tnx_headwise_product(_p(x), c_int(x_ld), c_int(x_head), _p(w if do_product else None), _p(out), c_int(out_ld),
+                                    c_int(out_head), _p(token_request), _p(positions), _p(inv_freq), c_int(rot_dims),
+                                    c_int(1 if interleaved else 0), c_int(pad_to), c_int(1 if do_product else 0), c_int(N),
+                                    c_int(n_heads), c_int(k), c_int(n_out), c_int(_is_h16(x)), _stream()), "headwise_product")
+
+
+def conv_state_update(proj, col0, state, ctx):
+    """The convolution state [slots, keep, channels] of every request with more than one row becomes its last `keep`
+    projected values (columns col0 .. col0 + channels of proj); requests with one row are left alone."""
+    lib = _lib("conv_qkv", proj, state)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    _need(state, "state", proj.dtype, 3)
+    keep, channels = state.shape[1], state.shape[2]
+    if col0 < 0 or col0 + channels > width:
+        raise KernelError("the projection is narrower than the state's channels")
+    _check(lib.tnx_conv_state_update(_p(proj), c_int(ld), c_int(col0), _p(state), c_int(keep), c_int(channels),
+                                     _p(ctx.q_start), _p(ctx.q_len), _p(ctx.state_slots), c_int(ctx.q_len.shape[0]),
+                                     c_int(_is_h16(proj)), _stream()), "conv_state_update")
+
+
+def delta_prep(proj, col0, b_off, a, conv_w, taps, state, ctx, a_log, dt_bias, unit_eps, q_scale, activation, q_out, k_out,
+               v_out, beta_out, g_out, n_heads, n_kv_heads, k_dim, v_dim):
+    """From the projections' output `proj` [N, *] (queries, keys, values side by side from column col0 on; the write
+    strengths' logits at b_off) and the decays' logits `a` [N, n_heads * k_dim] (32-bit): convolution (conv_w
+    [taps, channels] 32-bit, state [slots, taps - 1, channels] in proj's type) and activation, unit-norm q (times q_scale)
+    and k, beta = sigmoid, g = exp(-exp(a_log) softplus(a + dt_bias)); all outputs 32-bit."""
+    lib = _lib("delta_rule", proj)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    H, G, dk, dv = n_heads, n_kv_heads, k_dim, v_dim
+    C = 2 * G * dk + H * dv
+    if col0 < 0 or col0 + C > width or b_off < 0 or b_off + H > width:
+        raise KernelError("the projection is narrower than its columns")
+    _need(a, "a", torch.float32, None, contiguous=False)
+    if _rows_2d(a, "a")[:2] != (N, H * dk):
+        raise KernelError(f"a must be [{N}, {H * dk}]")
+    _need(conv_w, "conv_w", torch.float32, 2)
+    if tuple(conv_w.shape) != (taps, C):
+        raise KernelError(f"conv_w must be [{taps}, {C}]")
+    if taps > 1:
+        _need(state, "state", proj.dtype, 3)
+        if tuple(state.shape[1:]) != (taps - 1, C):
+            raise KernelError(f"state must be [slots, {taps - 1}, {C}]")
+    _f32_vec(a_log, "a_log", H); _f32_vec(dt_bias, "dt_bias", H * dk)
+    for t, nm, w in ((q_out, "q_out", G * dk), (k_out, "k_out", G * dk), (v_out, "v_out", H * dv), (beta_out, "beta_out", H),
+                     (g_out, "g_out", H * dk)):
+        _need(t, nm, torch.float32, 2)
+        if tuple(t.shape) != (N, w):
+            raise KernelError(f"{nm} must be [{N}, {w}]")
+    for t, nm in ((ctx.token_request, "token_request"), (ctx.positions, "positions"), (ctx.q_start, "q_start"),
+                  (ctx.q_len, "q_len"), (ctx.state_slots, "state_slots")):
+        _need(t, nm, torch.int32, 1)
+    _check(lib.tnx_delta_prep(_p(proj), c_int(ld), c_int(col0), c_int(b_off), _p(a), c_int(a.stride(0)), _p(conv_w),
+                              c_int(taps), _p(state if taps > 1 else None), _p(ctx.token_request), _p(ctx.positions),
+                              _p(ctx.q_start), _p(ctx.q_len), _p(ctx.state_slots), _p(a_log), _p(dt_bias), c_float(unit_eps),
+                              c_float(q_scale), c_int(activation_code(activation)), _p(q_out), _p(k_out), _p(v_out),
+                              _p(beta_out), _p(g_out), c_int(N), c_int(H), c_int(G), c_int(dk), c_int(dv),
+                              c_int(_is_h16(proj)), _stream()), "delta_prep")
+    if taps > 1 and not ctx.decode_only:
+        conv_state_update(proj, col0, state, ctx)
+
+
+def delta_scan(q, k, v, beta, g, state, q_start, q_len, state_slots, out, n_heads, n_kv_heads, k_dim, v_dim):
+    """Per request and head, over the request's rows of this step in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    out = S^T q.  All 32-bit; state [slots, n_heads, v_dim, k_dim]; q, k [N, n_kv_heads * k_dim]."""
+    lib = _build.load("delta_rule")
+    N = q.shape[0]
+    for t, nm, w in ((q, "q", n_kv_heads * k_dim), (k, "k", n_kv_heads * k_dim), (v, "v", n_heads * v_dim),
+                     (beta, "beta", n_heads), (g, "g", n_heads * k_dim), (out, "out", n_heads * v_dim)):
+        _need(t, nm, torch.float32, 2)
+        if tuple(t.shape) != (N, w):
+            raise KernelError(f"{nm} must be [{N}, {w}]")
+    _need(state, "state", torch.float32, 4)
+    if tuple(state.shape[1:]) != (n_heads, v_dim, k_dim):
+        raise KernelError(f"state must be [slots, {n_heads}, {v_dim}, {k_dim}]")
+    for t, nm in ((q_start, "q_start"), (q_len, "q_len"), (state_slots, "state_slots")):
+        _need(t, nm, torch.int32, 1)
+    _check(lib.tnx_delta_scan(_p(q), _p(k), _p(v), _p(beta), _p(g), _p(state), _p(q_start), _p(q_len), _p(state_slots),
+                              _p(out), c_int(q_len.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(k_dim), c_int(v_dim),
+                              _stream()), "delta_scan")

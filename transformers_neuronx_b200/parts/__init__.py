@@ -6,4 +6,5 @@ from .linear import Linear, linear_forward
 from . import norm, position, attention, feedforward, block, embedding   # register the built-in kinds
 from . import rotary_attention, retention, mingru, parallel, conv_attention   # noqa: F401  more built-in mixers
 from . import moe   # noqa: F401  the feed-forward of routed experts
+from . import latent_attention, delta_rule   # noqa: F401  attention through latents; the gated delta rule
 from .embedding import Embedding, Head

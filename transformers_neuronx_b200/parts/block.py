@@ -14,6 +14,11 @@ output_norm:                                              x = x + m norm1(mixer(
     itself.  The sublayer's result goes into a 32-bit buffer and the norm's kernel adds it to the stream
     (Norm.forward_add); a layer may have no feed-forward.
 
+sandwich_norm:                                            x = x + norm1_post(mixer(norm1(x))); x = x + norm2_post(ff(norm2(x)))
+    a norm before and after each sublayer (the layer's spec names the two further norms).  The sublayer's result
+    goes into a 32-bit buffer; one kernel normalises it, adds it to the stream and, where the next sublayer of the
+    same layer follows, applies that sublayer's input norm to the new row (Norm.forward_add(..., then=norm2)).
+
 `x` is the 32-bit residual stream and is updated in place; `x_act` is its copy in the activation
 type, which a block that feeds x itself into a matrix product needs on entry
 (``needs_act_input``) and keeps current (``keeps_act_current``).
@@ -123,7 +128,45 @@ class OutputNormBlock(ScaledPostNormBlock):
             self.norm2.forward_add(ctx, x, self.residual_scale, out, out_f32=x, out_act=x_act)
 
 
+class SandwichNormBlock(ScaledPostNormBlock):
+    """x <- x + norm1_post(mixer(norm1(x))), then x <- x + norm2_post(ff(norm2(x))); a layer may have no feed-forward."""
+    needs_act_input = False
+    keeps_act_current = False
+
+    def __init__(self, norm1, mixer, norm2, feed_forward, layer_spec=None):
+        from .registry import build_part
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self.norm1_post = build_part("norm", getattr(layer_spec, "norm1_post", None))
+        self.norm2_post = build_part("norm", getattr(layer_spec, "norm2_post", None)) if feed_forward is not None else None
+        need = [(norm1, "forward"), (self.norm1_post, "forward_add")]
+        if feed_forward is not None:
+            need += [(norm2, "forward"), (self.norm2_post, "forward_add")]
+        for n, method in need:
+            if n is None or not hasattr(n, method):
+                raise ValueError("a sandwich_norm block needs a norm before each sublayer and one that adds a normalised "
+                                 f"sublayer output to the stream behind it; {type(n).__name__} does not fit")
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm1_post, self.norm2, self.feed_forward, self.norm2_post)
+                if p is not None]
+
+    def forward(self, ctx, x, x_act):
+        N, W = x.shape
+        h = ctx.scratch(N, W)
+        self.norm1.forward(ctx, x, out_act=h)
+        out = ctx.scratch(N, W, x.dtype)
+        self._run(ctx, self.mixer, h, out)
+        if self.feed_forward is None:
+            self.norm1_post.forward_add(ctx, x, 1.0, out, out_f32=x)
+            return
+        # one kernel: the stream takes the normalised mixer output, and the new row is normalised for the feed-forward
+        self.norm1_post.forward_add(ctx, x, 1.0, out, out_f32=x, out_act=h, then=self.norm2)
+        self._run(ctx, self.feed_forward, h, out)
+        self.norm2_post.forward_add(ctx, x, 1.0, out, out_f32=x)
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("sandwich_norm", SandwichNormBlock)
 register_block("output_norm", OutputNormBlock)
 register_block("post_norm_scaled", ScaledPostNormBlock)
 register_block("post_norm", PostNormBlock)

@@ -14,6 +14,7 @@ from .spec import DenseFeedForwardSpec, GatedFeedForwardSpec
 class DenseFeedForward(FeedForward):
     graph_safe = True
     takes_normed_input = True       # `h` only feeds fc1
+    can_overwrite = True
     libraries = ("gemm_simt", "gemm_tc", "gemv")
 
     def __init__(self, spec: DenseFeedForwardSpec):
@@ -31,10 +32,10 @@ class DenseFeedForward(FeedForward):
     def parameter_bytes(self):
         return self.fc1.parameter_bytes() + self.fc2.parameter_bytes()
 
-    def forward(self, ctx, h, residual):
+    def forward(self, ctx, h, residual, accumulate=True):
         a = ctx.scratch(h.shape[0], self.spec.fc1.out_features)
         self.fc1.forward(h, a, activation=self.spec.activation)
-        self.fc2.forward(a, residual, residual=residual)
+        self.fc2.forward(a, residual, residual=residual if accumulate else None)
 
 
 class GatedDenseFeedForward(FeedForward):

@@ -79,10 +79,16 @@ class RMSNorm(Norm):
         ops.rms_norm(x, self.weight, self.spec.eps, out_f32=out_f32, out_act=out_act, x_scale=x_scale, delta=delta,
                      weight_offset=self.spec.weight_offset)
 
-    def forward_add(self, ctx, x, add_scale, delta, out_f32=None, out_act=None):
-        """x + add_scale * norm(delta) in one kernel (the norm on a sublayer's output alone); out_f32 may be x."""
+    def forward_add(self, ctx, x, add_scale, delta, out_f32=None, out_act=None, then=None):
+        """x + add_scale * norm(delta) in one kernel (the norm on a sublayer's output alone); out_f32 may be x.
+        `then` (another RMSNorm): out_act receives that norm of the new row instead of the row's copy."""
+        nxt = None
+        if then is not None:
+            if not isinstance(then, RMSNorm):
+                raise ValueError(f"only an RMS norm can follow inside the same kernel, not {type(then).__name__}")
+            nxt = (then.weight, then.spec.weight_offset, then.spec.eps)
         ops.rms_norm_add(x, add_scale, delta, self.weight, self.spec.eps, out_f32=out_f32, out_act=out_act,
-                         weight_offset=self.spec.weight_offset)
+                         weight_offset=self.spec.weight_offset, then=nxt)
 
 
 register_norm("layer_norm", LayerNorm)

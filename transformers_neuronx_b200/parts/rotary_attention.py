@@ -7,6 +7,8 @@
   rotate_values: v_j is turned by its position j over all v_dim dims before it is cached, and each head's
       output at position i is turned back by i: the sum then holds the values turned by j - i
   output projection with bias
+  a spec without a value projection: the values are the keys as projected (bias included), before their norm and
+      rotation; nothing more is computed for them, the same columns of the product are read twice
 
 Queries/keys (k_dim) and values (v_dim) may differ in size.  The cache's pages and the attention kernels take
 one head size, so q, k and v are written with D = max(k_dim, v_dim) rounded up to 16 dims a head, the rest zero:
@@ -48,7 +50,10 @@ class RotaryAttention(FusableMixer):
             raise ValueError(f"{s.rotary.dims} rotated dims do not fit heads of {s.k_dim}")
         if s.rotate_values and (s.rotary is None or s.v_dim % 2):
             raise ValueError("rotated values need a rotation and an even value size")
-        self.inputs = [Linear(s.q), Linear(s.k), Linear(s.v)]
+        self.values_are_keys = s.v is None
+        if self.values_are_keys and (s.v_dim != s.k_dim or s.rotate_values):
+            raise ValueError("values that are the keys have the keys' size and are not rotated")
+        self.inputs = [Linear(s.q), Linear(s.k)] + ([] if self.values_are_keys else [Linear(s.v)])
         self.output = Linear(s.out)
         self.q_weight = self.k_weight = self.head_scale = self.inv_freq_qk = self.inv_freq_v = None
 
@@ -86,7 +91,8 @@ class RotaryAttention(FusableMixer):
         H, G = s.n_heads, s.n_kv_heads
         q, k, v = ctx.scratch(N, H * D), ctx.scratch(N, G * D), ctx.scratch(N, G * D)
         k_off = col0 + H * s.k_dim
-        ops.rotary_qkv_prep(proj, col0, k_off, k_off + G * s.k_dim, ctx.token_request, ctx.positions, self.q_weight,
+        v_off = k_off if self.values_are_keys else k_off + G * s.k_dim
+        ops.rotary_qkv_prep(proj, col0, k_off, v_off, ctx.token_request, ctx.positions, self.q_weight,
                             self.k_weight, s.norm_eps, self.head_scale, self.inv_freq_qk,
                             s.rotary.dims if s.rotary is not None else 0, self.inv_freq_v, q, k, v, H, G, s.k_dim,
                             s.v_dim, D)

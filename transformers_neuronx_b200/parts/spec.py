@@ -101,6 +101,75 @@ class RotaryAttentionSpec:
     norm_eps: float = 1e-6
     head_scale: Optional[str] = None  # tensor [n_heads]: the score of head h is multiplied by its entry
     window: Optional[int] = None
+    # `v` None: there is no value projection; the values are the keys as projected (with bias), before normalisation
+    # and rotation (v_dim = k_dim)
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose queries and whose keys and values pass through low-rank latents, with a sliding window:
+      c_q = rms(W_dq h) * q_norm,  q = W_uq c_q, per head [k_dim unrotated, rot_dim rotated]
+      W_dkv h = [kv_rank | rot_dim]: c = rms(first part) * kv_norm (the latent), the rest one rotated key part that all
+      heads share;  per head  k = [W_uk c | rotated part],  v = W_uv c;  score = scale * <q, k>.
+    The rotated parts turn by position in interleaved pairs (2i, 2i + 1) or halves.  Only c and the rotated key part are
+    kept per position."""
+    kind: str                        # 'latent_attention'
+    hidden: int
+    n_heads: int
+    k_dim: int                       # unrotated query/key dims per head
+    rot_dim: int                     # rotated query/key dims per head (0: none)
+    v_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    dq: LinearSpec = None            # [q_rank, hidden]
+    uq: LinearSpec = None            # [n_heads * (k_dim + rot_dim), q_rank]
+    dkv: LinearSpec = None           # [kv_rank + rot_dim, hidden]
+    uk: str = None                   # tensor [n_heads * k_dim, kv_rank]
+    uv: str = None                   # tensor [n_heads * v_dim, kv_rank]
+    out: LinearSpec = None
+    q_norm: Optional[str] = None     # tensor [q_rank]
+    kv_norm: Optional[str] = None    # tensor [kv_rank]
+    norm_eps: float = 1e-6
+    rotary: Optional[RotarySpec] = None    # over the rot_dim part (rotary.dims = rot_dim)
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """A recurrence with an error-correcting write and a decay per key channel.  Per head, with S of k_dim x v_dim:
+        S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+    q, k (n_kv_heads x k_dim, shared by groups of heads) and v (n_heads x v_dim) pass a short causal convolution over
+    time and an activation; q and k are made unit vectors (x / sqrt(sum x^2 + unit_eps)), q times q_scale;
+    beta = sigmoid(W_b h); g = exp(-exp(A_log_h) softplus(W_a2 W_a1 h + dt_bias)) per head and key channel;
+    each head's o is divided by its root mean square, times `out_norm` (one weight vector of v_dim), times
+    sigmoid(W_g2 W_g1 h).  The inner sizes of a1/a2 and g1/g2 may be -1: they are then the stored tensors'."""
+    kind: str                        # 'delta_rule'
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    k_dim: int
+    v_dim: int
+    conv_taps: int
+    q: LinearSpec = None
+    k: LinearSpec = None
+    v: LinearSpec = None
+    beta: LinearSpec = None          # [n_heads, hidden]
+    a1: LinearSpec = None            # [rank_a, hidden]
+    a2: LinearSpec = None            # [n_heads * k_dim, rank_a]
+    g1: LinearSpec = None            # [rank_g, hidden]
+    g2: LinearSpec = None            # [n_heads * v_dim, rank_g]
+    out: LinearSpec = None
+    q_conv: Optional[str] = None     # tensors [channels, conv_taps]; the last column weighs the current token
+    k_conv: Optional[str] = None
+    v_conv: Optional[str] = None
+    a_log: str = None                # tensor [n_heads]
+    dt_bias: str = None              # tensor [n_heads * k_dim]
+    out_norm: Optional[str] = None   # tensor [v_dim]
+    norm_eps: float = 1e-6
+    unit_eps: float = 1e-6
+    q_scale: float = 1.0
+    conv_activation: str = "silu"
 
 
 @dataclass(frozen=True)
@@ -224,11 +293,13 @@ class DenseFeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    block: str                       # 'pre_norm' | 'post_norm' | 'post_norm_scaled' | 'output_norm' | a registered kind
+    block: str                       # 'pre_norm' | 'post_norm' | 'post_norm_scaled' | 'output_norm' | 'sandwich_norm' | a registered kind
     norm1: Any = None
     mixer: Any = None
     norm2: Any = None
     feed_forward: Any = None         # None: the layer has no feed-forward (and no second norm)
+    norm1_post: Any = None           # 'sandwich_norm': the norms on the sublayers' outputs,
+    norm2_post: Any = None           #     x <- x + norm1_post(mixer(norm1(x))); x <- x + norm2_post(ff(norm2(x)))
     residual_scale: float = 1.0      # 'post_norm_scaled': x <- norm(residual_scale * x + sublayer(x));
                                      # 'output_norm': x <- x + residual_scale * norm(sublayer(x))
 

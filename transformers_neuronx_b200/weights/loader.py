@@ -25,7 +25,7 @@ from .model_files import open_model_files
 @dataclass(frozen=True)
 class TensorSpec:
     name: str                      # name in the checkpoint
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]         # an entry of -1: any size (the part takes it from the stored tensor)
     kind: str = "matrix"           # 'matrix' | 'table' | 'bias' | 'norm_weight' | 'norm_bias' | 'int_table'
     tied_to: Optional[str] = None  # when absent from the file, this other tensor is used
     optional: bool = False         # may be absent without a tie (never used by OPT)
@@ -86,7 +86,7 @@ def match_tensors(specs: Sequence[TensorSpec], available: Dict[str, Tuple[torch.
         used.add(found)
         resolved[s.name] = found
         got = tuple(available[found][1])
-        if got != tuple(s.shape):
+        if len(got) != len(s.shape) or any(w >= 0 and g != w for g, w in zip(got, s.shape)):
             wrong.append((s.name, got, s.shape))
     for s in specs:           # ties are resolved after their targets
         if s.name not in resolved and s.tied_to is not None:

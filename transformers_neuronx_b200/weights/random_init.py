@@ -26,6 +26,9 @@ def random_tensors(specs: Sequence[TensorSpec], seed: int, init_std: float,
     for s in specs:
         if s.tied_to is not None:
             continue                      # a tied tensor is not stored
+        if any(n < 0 for n in s.shape):
+            raise ValueError(f"{s.name}: a size that is left to the stored tensor cannot be drawn at random; "
+                             "name it in the configuration")
         if s.kind == "int_table":
             out[s.name] = torch.zeros(s.shape, dtype=torch.int32)
             continue
