@@ -18,7 +18,9 @@ OPT-30B sizes decoding at batch 16, and OPT-13B sizes serving 32 requests with a
 `--workload vononex` (a line of its own, not part of the default one): prefill and decode of the Vononex decoder at
 two widths beside OPT at the same width, with every kernel family's time.  `--workload pifelix`: the same for the
 Pifelix decoder (attention behind convolved projections under a chunked mask, two of four layers reading another
-layer's pages, eight experts of which a token runs two).
+layer's pages, eight experts of which a token runs two).  `--workload tutelix`: the Tutelix decoder (windowed
+attention whose values are its keys, attention through latents, a gated delta-rule recurrence) beside Vononex, the
+closest design here (paged attention beside a recurrence with a state of fixed size), at the same widths.
 """
 from __future__ import annotations
 
@@ -409,6 +411,33 @@ def pifelix_config(size):
             "norm": {"eps": 1e-5}, "init_std": 0.02, "max_positions": CONTEXT, "layers": layers}
 
 
+# ---- the Tutelix decoder beside Vononex at equal sizes -----------------------------------------------
+# Heads of 128 dims on a quarter as many key heads with half of each head rotated; a latent layer whose position holds
+# 96 + 32 numbers (the widest the tensor-core prefill kernel takes; "wide": 192 + 64, the widest any kernel takes) behind
+# a query latent of 3/8 the width; a recurrence with states of 128 x 128 a head, query/key heads shared four ways, four
+# taps and low-rank decays and gates of 64; windows as long as the bench's context (every key is read, as in the
+# decoder beside it); a feed-forward of 4x the width (two matrices: the parameters of Vononex's gated 8/3 one).
+TUTELIX_SIZES = {"2048": dict(width=2048, heads=16, kv=4, ff=8192, latent=(96, 32)),
+                 "4096": dict(width=4096, heads=32, kv=8, ff=16384, latent=(96, 32)),
+                 "2048wide": dict(width=2048, heads=16, kv=4, ff=8192, latent=(192, 64))}
+TUTELIX_LAYERS = ("attention", "latent_attention", "channel_delta", "attention")
+
+
+def tutelix_config(size):
+    z = TUTELIX_SIZES[size]
+    H, rank, rot = z["heads"], z["latent"][0], z["latent"][1]
+    mixers = {"attention": {"heads": H, "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                            "mask": {"size": CONTEXT}, "rot": {"dims": 64, "base": 5e5}},
+              "latent_attention": {"heads": H, "dim": 128, "rot_dim": rot, "vdim": 128, "q_rank": 3 * z["width"] // 8,
+                                   "kv_rank": rank, "scale": (128 + rot) ** -0.5, "mask": {"size": CONTEXT},
+                                   "rot": {"dims": rot, "base": 1e4}},
+              "channel_delta": {"heads": H, "kv_heads": z["kv"], "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64,
+                                "gate_rank": 64}}
+    return {"architecture": "Tutelix", "vocab": 50272, "width": z["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "init_std": 0.02, "max_positions": CONTEXT,
+            "layers": [{"type": t, "mixer": mixers[t], "mlp": {"kind": "dense", "ff": z["ff"]}} for t in TUTELIX_LAYERS]}
+
+
 def build_vononex(size, dtype="bfloat16", config=None):
     import torch
     from transformers_neuronx_b200.config import config_from_dict
@@ -480,7 +509,14 @@ def workload_pifelix(steps, warmup, sizes=None, only=None, batch=8):
                             config=pifelix_config)
 
 
-def workload_vononex(steps, warmup, sizes=None, only=None, batch=8, design="vononex", table=None, layers=None, config=None):
+def workload_tutelix(steps, warmup, sizes=None, only=None, batch=8):
+    """workload_vononex for the Tutelix decoder, with Vononex at the same width beside it instead of OPT."""
+    return workload_vononex(steps, warmup, sizes or ["2048", "4096"], only, batch, design="tutelix", table=TUTELIX_SIZES,
+                            layers=TUTELIX_LAYERS, config=tutelix_config, beside="vononex")
+
+
+def workload_vononex(steps, warmup, sizes=None, only=None, batch=8, design="vononex", table=None, layers=None, config=None,
+                     beside="opt"):
     """Prefill (one 2,048-token prompt) and decode (batch 1, 8, 64, contexts ending at 2,048) of a four-layer
     Vononex decoder, and of a four-layer OPT decoder of the same width and heads, in bfloat16 with random
     weights; per layer, with the decode step's share of the memory roofline and every kernel family's time."""
@@ -500,10 +536,15 @@ def workload_vononex(steps, warmup, sizes=None, only=None, batch=8, design="vono
         z = table[size]
         opt_cfg = dict(OPT_6_7B, hidden_size=z["width"], num_attention_heads=z["heads"], ffn_dim=4 * z["width"],
                        word_embed_proj_dim=z["width"])
-        for which in (design, "opt"):
+        for which in (design, beside):
             if which == design:
                 model, cfg = build_vononex(size, config=config)
                 tables = cfg.vocab * cfg.width * 2                    # the embedding table: rows of the batch only
+            elif which == "vononex":
+                if str(z["width"]) in {k.split("_")[1] for k in rows if k.startswith("vononex_")}:
+                    continue                                          # this width stands in the table already
+                model, cfg = build_vononex(str(z["width"]))
+                tables, size = cfg.vocab * cfg.width * 2, str(z["width"])
             else:
                 model, cfg = build(len(layers), dtype="bfloat16", base=opt_cfg)
                 tables = (cfg.max_position_embeddings + 2) * cfg.hidden_size * 2      # the output matrix is the token table
@@ -530,6 +571,8 @@ def extra_workload(name, steps, warmup, sizes=None, only=None, batch=8):
         res = workload_vononex(steps, warmup, sizes, only, batch)
     elif name == "pifelix":
         res = workload_pifelix(steps, warmup, sizes, only, batch)
+    elif name == "tutelix":
+        res = workload_tutelix(steps, warmup, sizes, only, batch)
     elif name == "family":
         res = workload_family(steps, warmup, sizes)
     elif name == "sweep":
@@ -565,10 +608,10 @@ def main():
     ap.add_argument("--skip-large", action="store_true", help="leave out the OPT-13B and OPT-30B workloads")
     ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
                     help="the serving type (float16 is what OPT checkpoints are stored in)")
-    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep", "vononex", "pifelix"],
+    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep", "vononex", "pifelix", "tutelix"],
                     help="run one of the further workloads instead of the default line")
     ap.add_argument("--sizes", default=None, help="for --workload family: comma-separated sizes (default: all of 125m .. 66b); for --workload vononex: "
-                    "widths (2048, 4096)")
+                    "widths (2048, 4096); for --workload tutelix: 2048, 4096, 2048wide")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run just this part and print its time (for profiling a small case)")
     a = ap.parse_args()

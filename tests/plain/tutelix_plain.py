@@ -28,11 +28,15 @@ def rms(x, eps, w=None):
 
 def turn(x, positions, dims, base, interleaved):
     """x [T, heads, d]: the first `dims` dims of every head turned by position * base^(-2i/dims); pair i is
-    (2i, 2i + 1) when interleaved, else (i, i + dims/2)."""
+    (2i, 2i + 1) when interleaved, else (i, i + dims/2).  The design forms positions and angles in 32-bit: the
+    frequency and the product are rounded to 32-bit here as well (at position 180 an angle's 32-bit rounding alone moves
+    the logits by 4e-5), sine and cosine of that angle are 64-bit."""
     y = x.clone()
+    f32 = lambda z: float(torch.tensor(z, dtype=torch.float32))
+    freq = [f32(base ** (-2.0 * i / dims)) for i in range(dims // 2)]
     for t, p in enumerate(positions):
         for i in range(dims // 2):
-            a_ = p * base ** (-2.0 * i / dims)
+            a_ = f32(float(p) * freq[i])
             c, s = math.cos(a_), math.sin(a_)
             ia, ib = (2 * i, 2 * i + 1) if interleaved else (i, i + dims // 2)
             u, v = x[t, :, ia], x[t, :, ib]
@@ -107,6 +111,22 @@ def unit(x):
     return x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
 
 
+def delta_recurrence(q, k, v, beta, decay):
+    """q, k [T, G, d], v [T, H, dv], beta [T, H], decay [T, H, d] -> o [T, H, dv].  Per head, with S of d x dv from zero:
+    S <- decay_t * S (row i by decay_t[i]); u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t."""
+    T, H, dv, G, d = v.shape[0], v.shape[1], v.shape[2], k.shape[1], k.shape[2]
+    o = torch.zeros(T, H, dv, dtype=F64)
+    for hd in range(H):
+        g = hd // (H // G)
+        S = torch.zeros(d, dv, dtype=F64)
+        for tt in range(T):
+            S = decay[tt, hd][:, None] * S
+            u = beta[tt, hd] * (v[tt, hd] - S.T @ k[tt, g])
+            S = S + torch.outer(k[tt, g], u)
+            o[tt, hd] = S.T @ q[tt, g]
+    return o
+
+
 def gated_delta(h, t, p, m, eps):
     T, H, G, d, dv = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = unit(short_conv_silu(h @ t[p + "q"].T, t[p + "q.conv"]).view(T, G, d)) * d ** -0.5
@@ -117,16 +137,7 @@ def gated_delta(h, t, p, m, eps):
     step = torch.nn.functional.softplus((h @ t[p + "a1"].T) @ t[p + "a2"].T + t[p + "dt_bias"]).view(T, H, d)
     decay = torch.exp(-rate * step)                                                  # [T, H, d]
     gate = torch.sigmoid((h @ t[p + "g1"].T) @ t[p + "g2"].T).view(T, H, dv)
-    o = torch.zeros(T, H, dv, dtype=F64)
-    for hd in range(H):
-        g = hd // (H // G)
-        S = torch.zeros(d, dv, dtype=F64)
-        for tt in range(T):
-            S = decay[tt, hd][:, None] * S
-            u = beta[tt, hd] * (v[tt, hd] - S.T @ k[tt, g])
-            S = S + torch.outer(k[tt, g], u)
-            o[tt, hd] = S.T @ q[tt, g]
-    o = rms(o, eps, t[p + "norm"]) * gate
+    o = rms(delta_recurrence(q, k, v, beta, decay), eps, t[p + "norm"]) * gate
     return o.reshape(T, H * dv) @ t[p + "o"].T
 
 

@@ -62,6 +62,9 @@ struct Params {
     int sk_pairs;                // ... over the first sk_pairs pairs
     const int* group_of_tile;    // grouped product: the group of every tile of tokens (128 of them, or BN in the swapped form), -1: none;
     int group_rows;              //   W holds group_rows rows per group, a tile of group g reads W's rows from g * group_rows on
+    int batch_w_step;            // batched product (not swapped, K not split): blockIdx.z = b multiplies the columns of A from
+    int batch_a_step;            //   b * batch_a_step on with W's rows from b * batch_w_step on and writes the columns of C from
+    int batch_c_step;            //   b * batch_c_step on; 0: not batched (blockIdx.z is the K split)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -363,7 +366,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     __shared__ int last_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_p = blockIdx.x, tile_q = blockIdx.y, split = blockIdx.z;
+    const int tile_p = blockIdx.x, tile_q = blockIdx.y;
+    const int batch = (!SWAP && p.batch_w_step) ? (int)blockIdx.z : 0, split = (!SWAP && p.batch_w_step) ? 0 : (int)blockIdx.z;
     // A grouped product: every tile of tokens belongs to one group (an expert) and multiplies that group's rows of W.
     // Which group is written by the kernel before this one, so it is read behind the dependency wait; a tile without
     // a group has nothing to do (nothing has been set up yet, so the whole CTA may leave).
@@ -375,6 +379,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         if (g < 0) return;
         if (SWAP) p_row0 += g * p.group_rows; else q_row0 += g * p.group_rows;
     }
+    q_row0 += batch * p.batch_w_step;
     // Split K summed in a cluster, swapped form, 2, 4 or 8 splits: every CTA sends the bands of its partial tile
     // to their owners (one bulk copy from shared memory to shared memory each) and adds up what it receives
     // with plain shared-memory loads.  The staging area (a tile) and the receive area (S - 1 bands of it) must
@@ -405,7 +410,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
         const int kx = (kb_begin + i) * BLOCK_K;
         if (SWAP) tma_load_2d(a_dst + A_BYTES, &map_q, &full_bar[s], kx, tile_q * BN);
-        else tma_load_2d(a_dst, &map_p, &full_bar[s], kx, tile_p * TILE_P);
+        else tma_load_2d(a_dst, &map_p, &full_bar[s], kx + batch * p.batch_a_step, tile_p * TILE_P);
     };
     pdl_launch_dependents();
     int issued = 0;
@@ -499,6 +504,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         const int lane_row = tile_p * TILE_P + row_in_tile;
         if (ok) {
             if (p.splits == 1) {
+                Params pc = p;                       // a batched product writes its own columns of C
+                if (batch) pc.C = (char*)p.C + (size_t)batch * p.batch_c_step * (p.c_is_h16 ? 2 : 4);
 #pragma unroll 1
                 for (int c = 0; c < BN; c += LD_COLS) {
                     uint32_t r[32];
@@ -508,7 +515,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = (j < LD_COLS && num_kb > 0) ? __uint_as_float(r[j]) : 0.f;
-                    store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
+                    store_tile_row<BN, SWAP>(pc, lane_row, tile_q * BN + c, v, LD_COLS);
                 }
             } else if (p.cluster_reduce && !sum_by_push) {
                 // 32-bit partial tile -> this CTA's shared memory, [col 0..BN)[row 0..127], over the
@@ -1577,6 +1584,29 @@ TNX_EXPORT int tnx_gemm_tc_grouped(const void* A, const void* W, void* C, int M,
     }
     if (!make_map(&mq, W, groups * N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
     return launch<128, 6, false>(mp, mq, p, dim3(M / TILE_P, (N + 127) / 128, 1), stream);
+}
+
+// A batched product: C[m, b * c_step + n] = sum_k A[m, b * a_step + k] W[b * N + n, k] for b < batches, n < N, k < K, in one
+// launch (blockIdx.z = b): per-head products of activations that lie head by head in their rows.  A is [M, lda] and C
+// [M, ldc] (16-bit or 32-bit), W holds the batches' [N, K] matrices one after the other.  A K block of 64 may reach past
+// K: W is zero there, so the caller sees to it that what A holds there is finite (K rounded up to 64 stays inside the
+// batch's own a_step columns).  The steps are multiples of 8 elements (16-byte accesses).
+TNX_EXPORT int tnx_gemm_tc_batched(const void* A, const void* W, void* C, int M, int N, int K, int batches, int lda, int a_step,
+                                   int ldc, int c_step, int c_h16, int* err_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batches <= 0) return 0;
+    if (K <= 0 || K % 8 || lda % 8 || a_step % 8 || c_step % 8 || ldc % 8 || batches > 65535) return TNX_ERR_UNSUPPORTED;
+    if ((K + BLOCK_K - 1) / BLOCK_K * BLOCK_K > a_step || c_step < N || (long long)batches * a_step > lda ||
+        (long long)(batches - 1) * c_step + N > ldc)
+        return TNX_ERR_UNSUPPORTED;
+    if ((((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) || (long long)batches * N >= (1ll << 31)) return TNX_ERR_UNSUPPORTED;
+    if (!err_word) return TNX_ERR_BAD_ARG;
+    Params p{};
+    p.K = K; p.ldc = ldc; p.act = TNX_ACT_NONE; p.c_is_h16 = c_h16; p.C = C; p.err = err_word;
+    p.rows_p = M; p.rows_q = N; p.splits = 1; p.kb_per_split = (K + BLOCK_K - 1) / BLOCK_K;
+    p.batch_w_step = N; p.batch_a_step = a_step; p.batch_c_step = c_step;
+    CUtensorMap mp, mq;
+    if (!make_map(&mp, A, M, batches * a_step, lda, TILE_P) || !make_map(&mq, W, batches * N, K, K, 128)) return TNX_ERR_UNSUPPORTED;
+    return launch<128, 6, false>(mp, mq, p, dim3((M + TILE_P - 1) / TILE_P, (N + 127) / 128, batches), stream);
 }
 
 // The same for groups of few rows: the swapped form (the group's rows of W fill the 128-row operand, `bn` = 16, 32, 64 or

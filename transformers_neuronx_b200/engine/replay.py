@@ -26,7 +26,7 @@ from .loading import load_model
 from .step import StepEntry, StepRunner
 
 
-def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None, out=None) -> int:
+def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None, out=None, max_requests: int = 4) -> int:
     # readline, not iteration: a step must be read as soon as its line is there (the sender waits
     # for `done` before it writes the next one)
     lines = iter(sys.stdin.readline, "") if lines is None else lines
@@ -36,7 +36,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
     ecfg = EngineConfig(dtype=dtype)
     page = ecfg.page_size
     num_pages = max(1, -(-int(max_tokens) // page))
-    runner = StepRunner(model, page_size=page, num_pages=num_pages, max_slots=8,
+    runner = StepRunner(model, page_size=page, num_pages=num_pages, max_slots=int(max_requests),
                         max_model_len=model.spec.max_positions, use_cuda_graphs=True)
     for line in lines:
         line = line.strip()
@@ -71,8 +71,10 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each request rounded up to 64)")
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="most requests that are live at any time: the slots for state of fixed size (default 4)")
     a = ap.parse_args(argv)
-    return replay(a.model, a.dtype, a.out, a.max_tokens)
+    return replay(a.model, a.dtype, a.out, a.max_tokens, max_requests=a.max_requests)
 
 
 if __name__ == "__main__":

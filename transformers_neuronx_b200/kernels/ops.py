@@ -970,6 +970,37 @@ def gemm_tc_grouped(a, w, out, group_of_tile, tile=128, used_tiles=0):
                                    c_int(_is_h16(out)), _p(group_of_tile), _p(st["err"]), _stream()), "gemm_tc_grouped")
 
 
+def gemm_tc_batched_supported(x, x_head, w, out, out_head) -> bool:
+    """What gemm_tc_batched takes: one 16-bit type, head pitches and row pitches that are multiples of 8 elements,
+    16-byte aligned bases, and K rounded up to 64 inside a head's own columns of x."""
+    if x.dtype not in _H16 or w.dtype != x.dtype or out.dtype != x.dtype or w.dim() != 3 or not w.is_contiguous():
+        return False
+    H, n_out, k = w.shape
+    if k % 8 or x_head % 8 or out_head % 8 or x.stride(0) % 8 or out.stride(0) % 8 or x.stride(1) != 1 or out.stride(1) != 1:
+        return False
+    if -(-k // 64) * 64 > x_head or out_head < n_out or H * x_head > x.stride(0) or H * out_head > out.stride(0):
+        return False
+    return x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+
+
+def gemm_tc_batched(x, x_head, w, out, out_head):
+    """out[n, h * out_head + c] = sum_i x[n, h * x_head + i] * w[h, c, i] for every head h in ONE launch of the tcgen05
+    product (w [heads, n_out, k], 32-bit sums).  The columns of x between k and k rounded up to 64 are read (against
+    zeros of w): they must hold finite numbers."""
+    lib = _lib("gemm_tc", x, w, out)
+    if not gemm_tc_batched_supported(x, x_head, w, out, out_head):
+        raise KernelError("gemm_tc_batched: a 16-bit type, pitches that are multiples of 8, 16-byte aligned bases, and k "
+                          "rounded up to 64 within a head's columns")
+    H, n_out, k = w.shape
+    N = x.shape[0]
+    if out.shape[0] != N:
+        raise KernelError("x and out differ in rows")
+    st = _state(x.device)
+    _check(lib.tnx_gemm_tc_batched(_p(x), _p(w), _p(out), c_int(N), c_int(n_out), c_int(k), c_int(H), c_int(x.stride(0)),
+                                   c_int(x_head), c_int(out.stride(0)), c_int(out_head), c_int(1), _p(st["err"]), _stream()),
+           "gemm_tc_batched")
+
+
 def moe_grouped(ctx, h, gate_up, down, ids, weights, out, gate_max, up_min, up_max, alpha, up_shift, weight_on_input=True,
                 accumulate=False):
     """moe_experts for many rows: the (row, expert) pairs sorted by expert into 128-row tiles, the experts' two

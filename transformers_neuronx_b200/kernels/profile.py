@@ -22,7 +22,7 @@ _NAMES = ("embed", "gather_rows", "patch_tokens", "layer_norm", "pick_rows", "ge
           "attention_simt", "attention_decode", "attention_prefill", "attention_prefill_tc", "sample", "sample_packed",
           "rms_norm", "rotary_qkv_prep", "rotary_unrotate", "retention_prep", "retention_scan", "retention_decode", "headwise_gated_rms_norm",
           "mingru_scan", "gated_activation", "rms_norm_add", "conv_qkv_prep", "moe_route", "moe_experts", "moe_sort_rows",
-          "gemm_tc_grouped", "moe_activation", "moe_combine")
+          "gemm_tc_grouped", "moe_activation", "moe_combine", "latent_prep", "headwise_product", "delta_prep", "delta_scan")
 
 
 class KernelProfile:

@@ -13,8 +13,9 @@ attention every other attention part uses (tcgen05 prefill, split decode with it
 all query heads on the one key/value head.
 
 The down projections of queries and of keys/values are one product; the two norms, the rotation of r and the rows'
-layout are one kernel; the per-head products run on the tensor cores head by head where there are enough tokens,
-else in one kernel that reads a head's matrix once for eight tokens.
+layout are one kernel; the per-head products run as ONE batched tensor-core product (a launch for all heads) where
+there are enough tokens and the sizes allow 16-byte accesses, else in one kernel that reads a head's matrix once for
+eight tokens.
 """
 from __future__ import annotations
 
@@ -29,7 +30,7 @@ from .registry import register_mixer
 from .rotary import inverse_frequencies
 from .spec import LatentAttentionSpec
 
-TENSOR_CORE_TOKENS = 64          # from this many tokens on the per-head products run as tensor-core products, head by head
+TENSOR_CORE_TOKENS = 64          # from this many tokens on the per-head products run as one batched tensor-core product
 
 
 class LatentAttention(Mixer):
@@ -99,18 +100,15 @@ class LatentAttention(Mixer):
         return PagedKVNeed(1, self.pad_dim, self.spec.window)
 
     def _per_head(self, ctx, x, x_head, w, w_t, out, out_head, k, n_out, **tail):
-        """out[:, h] = x[:, h, :k] W_h for every head: tensor-core products head by head for many tokens (where the
-        slices' addresses allow), else one kernel; the rotated tail and the padding, if any, by that kernel either way."""
+        """out[:, h] = x[:, h, :k] W_h for every head: one batched tensor-core product for many tokens (where the sizes
+        allow; it reads x up to k rounded up to 64 within a head, which the callers' buffers hold as finite numbers), else
+        one kernel; the rotated tail and the padding, if any, by that kernel either way."""
         H, N = self.spec.n_heads, x.shape[0]
-        if w_t is not None and N >= TENSOR_CORE_TOKENS:
-            views = [(x[:, h * x_head:h * x_head + k], w_t[h], out[:, h * out_head:h * out_head + n_out]) for h in range(H)]
-            if all(ops.gemm_tc_supported(a, wh, o) and o.stride(0) % 8 == 0 and o.data_ptr() % 16 == 0 for a, wh, o in views):
-                for a, wh, o in views:
-                    ops.gemm_tc(a, wh, o)
-                if tail:
-                    ops.headwise_product(x, x_head, None, out, out_head, ctx.token_request, H, k, n_out, do_product=False,
-                                         **tail)
-                return
+        if w_t is not None and N >= TENSOR_CORE_TOKENS and ops.gemm_tc_batched_supported(x, x_head, w_t, out, out_head):
+            ops.gemm_tc_batched(x, x_head, w_t, out, out_head)       # all heads in one launch
+            if tail:
+                ops.headwise_product(x, x_head, None, out, out_head, ctx.token_request, H, k, n_out, do_product=False, **tail)
+            return
         ops.headwise_product(x, x_head, w, out, out_head, ctx.token_request, H, k, n_out, **tail)
 
     def forward(self, ctx, h, out, accumulate=True):
