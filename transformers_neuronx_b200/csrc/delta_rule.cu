@@ -17,6 +17,7 @@
 // tnx_delta_scan: a thread block owns C columns (value dims) of one head of one request and walks the request's tokens
 //   of this step in order, the state's columns in registers: a column's k_dim rows are spread over R adjacent lanes,
 //   which add their partial sums of S^T k, S^T q and q.k with shuffles (one round for all three: o = (gS)^T q + (q.k) u).
+//   The tokens' inputs reach shared memory by asynchronous copies, a stage ahead of the walk.
 //   The state is stored [slot, head, v_dim, k_dim] (a column's rows side by side).
 #include "common.cuh"
 
@@ -82,19 +83,32 @@ delta_prep_kernel(const T* __restrict__ proj, int ld, int col0, int b_off, const
     }
 }
 
-// tokens whose inputs are staged in shared memory at a time (fewer for the longest keys: 48 KB of static shared memory)
-__host__ __device__ constexpr int scan_stage(int dkp) { return dkp > 128 ? 8 : 16; }
+// tokens whose inputs are staged in shared memory at a time, in each of two buffers (24 KB of keys, queries and decays)
+__host__ __device__ constexpr int scan_stage(int dkp) { return dkp > 128 ? 4 : dkp > 64 ? 8 : 16; }
+
+// Asynchronous copies global -> shared; `bytes_src` 0 fills the destination with zeros and reads nothing.
+__device__ __forceinline__ void cp_async4(float* dst, const float* src, bool take) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+                 "r"(take ? 4u : 0u) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src, bool take) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+                 "r"(take ? 16u : 0u) : "memory");
+}
 
 // KPT: rows of a column one thread keeps; R: lanes a column's rows are spread over (KPT * R >= k_dim); a block of 128
-// threads owns 128 / R columns.
-template <int KPT, int R>
+// threads owns 128 / R columns.  The tokens' inputs come in stages through two buffers: while one stage is walked, the
+// next one's copies are in flight, so the walk waits for memory once, at the first stage.  VEC: k_dim is a multiple
+// of 4 and the rows are 16-byte aligned (16-byte copies).
+template <int KPT, int R, bool VEC>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state,
                   const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ state_slots,
                   float* __restrict__ out, int H, int G, int dk, int dv) {
-    constexpr int DKP = KPT * R, C = 128 / R, SCAN_STAGE = scan_stage(KPT * R);
-    __shared__ float qs[SCAN_STAGE][DKP], ks[SCAN_STAGE][DKP], gs[SCAN_STAGE][DKP], vs[SCAN_STAGE][C], bs[SCAN_STAGE];
+    constexpr int DKP = KPT * R, C = 128 / R, ST = scan_stage(KPT * R);
+    __shared__ __align__(16) float qs[2][ST][DKP], ks[2][ST][DKP], gs[2][ST][DKP];
+    __shared__ float vs[2][ST][C], bs[2][ST];
     pdl_launch_dependents();
     pdl_wait();
     const int req = blockIdx.z, h = blockIdx.y;
@@ -106,49 +120,77 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     const int jl = threadIdx.x / R, r = threadIdx.x % R;
     const int j = blockIdx.x * C + jl;
     const bool col = j < dv;
+
+    auto fetch = [&](int t0, int buf) {               // the inputs of tokens t0 .. t0 + ST - 1 of this request's rows
+        const int nt = min(ST, len - t0);
+        if (VEC) {
+            for (int e = threadIdx.x; e < nt * (DKP / 4); e += 128) {
+                const int tt = e / (DKP / 4), i = (e % (DKP / 4)) * 4;
+                const size_t t = (size_t)(t_first + t0 + tt);
+                const bool in = i < dk;
+                cp_async16(&qs[buf][tt][i], in ? q + (t * G + kvh) * dk + i : q, in);
+                cp_async16(&ks[buf][tt][i], in ? k + (t * G + kvh) * dk + i : k, in);
+                cp_async16(&gs[buf][tt][i], in ? g + (t * H + h) * dk + i : g, in);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * DKP; e += 128) {
+                const int tt = e / DKP, i = e % DKP;
+                const size_t t = (size_t)(t_first + t0 + tt);
+                const bool in = i < dk;
+                cp_async4(&qs[buf][tt][i], in ? q + (t * G + kvh) * dk + i : q, in);
+                cp_async4(&ks[buf][tt][i], in ? k + (t * G + kvh) * dk + i : k, in);
+                cp_async4(&gs[buf][tt][i], in ? g + (t * H + h) * dk + i : g, in);
+            }
+        }
+        for (int e = threadIdx.x; e < nt * C; e += 128) {
+            const int tt = e / C, c = blockIdx.x * C + e % C;
+            cp_async4(&vs[buf][tt][e % C], c < dv ? v + ((size_t)(t_first + t0 + tt) * H + h) * dv + c : v, c < dv);
+        }
+        if (threadIdx.x < nt) cp_async4(&bs[buf][threadIdx.x], beta + (size_t)(t_first + t0 + threadIdx.x) * H + h, true);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    fetch(0, 0);
     float* st = state + (((size_t)slot * H + h) * dv + (col ? j : 0)) * dk;
     float S[KPT];
 #pragma unroll
     for (int m = 0; m < KPT; ++m) S[m] = (col && r + R * m < dk) ? st[r + R * m] : 0.f;
-    for (int t0 = 0; t0 < len; t0 += SCAN_STAGE) {
-        const int nt = min(SCAN_STAGE, len - t0);
-        __syncthreads();                              // the stage before is no longer read
-        for (int e = threadIdx.x; e < nt * DKP; e += 128) {
-            const int tt = e / DKP, i = e % DKP;
-            const size_t t = (size_t)(t_first + t0 + tt);
-            const bool in = i < dk;
-            qs[tt][i] = in ? q[(t * G + kvh) * dk + i] : 0.f;
-            ks[tt][i] = in ? k[(t * G + kvh) * dk + i] : 0.f;
-            gs[tt][i] = in ? g[(t * H + h) * dk + i] : 0.f;
+    int buf = 0;
+    for (int t0 = 0; t0 < len; t0 += ST, buf ^= 1) {
+        const int nt = min(ST, len - t0);
+        if (t0 + ST < len) {
+            fetch(t0 + ST, buf ^ 1);                  // the buffer that the stage before this one used: all have left it
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        for (int e = threadIdx.x; e < nt * C; e += 128) {
-            const int tt = e / C, c = blockIdx.x * C + e % C;
-            vs[tt][e % C] = c < dv ? v[((size_t)(t_first + t0 + tt) * H + h) * dv + c] : 0.f;
-        }
-        if (threadIdx.x < nt) bs[threadIdx.x] = beta[(size_t)(t_first + t0 + threadIdx.x) * H + h];
-        __syncthreads();
+        __syncthreads();                              // every thread's copies of this stage have landed
         for (int tt = 0; tt < nt; ++tt) {
-            float sk = 0.f, sq = 0.f, qk = 0.f;
+            float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, qk = 0.f;
+            float Sg[KPT];
+            // the decayed state first, then its products with k and q, in two chains each (half the dependent adds)
 #pragma unroll
             for (int m = 0; m < KPT; ++m) {
                 const int i = r + R * m;
-                const float kk = ks[tt][i], qq = qs[tt][i];
-                S[m] *= gs[tt][i];
-                sk = fmaf(kk, S[m], sk);
-                sq = fmaf(qq, S[m], sq);
+                const float kk = ks[buf][tt][i], qq = qs[buf][tt][i], gg = gs[buf][tt][i];
+                Sg[m] = S[m] * gg;
+                if (m & 1) { sk1 = fmaf(kk, Sg[m], sk1); sq1 = fmaf(qq, Sg[m], sq1); }
+                else { sk0 = fmaf(kk, Sg[m], sk0); sq0 = fmaf(qq, Sg[m], sq0); }
                 qk = fmaf(qq, kk, qk);
             }
+            float sk = sk0 + sk1, sq = sq0 + sq1;
 #pragma unroll
             for (int o = R >> 1; o > 0; o >>= 1) {    // the R lanes of a column are neighbours in one warp
                 sk += __shfl_xor_sync(0xffffffffu, sk, o);
                 sq += __shfl_xor_sync(0xffffffffu, sq, o);
                 qk += __shfl_xor_sync(0xffffffffu, qk, o);
             }
-            const float u = bs[tt] * (vs[tt][jl] - sk);
+            const float u = bs[buf][tt] * (vs[buf][tt][jl] - sk);
 #pragma unroll
-            for (int m = 0; m < KPT; ++m) S[m] = fmaf(ks[tt][r + R * m], u, S[m]);
+            for (int m = 0; m < KPT; ++m) S[m] = fmaf(ks[buf][tt][r + R * m], u, Sg[m]);
             if (r == 0 && col) out[((size_t)(t_first + t0 + tt) * H + h) * dv + j] = fmaf(qk, u, sq);
         }
+        __syncthreads();                              // the stage is no longer read: the next fetch may overwrite it
     }
     if (col) {
 #pragma unroll
@@ -193,9 +235,14 @@ TNX_EXPORT int tnx_delta_scan(const float* q, const float* k, const float* v, co
 #define DSCAN(KPT, R)                                                                                                   \
     do {                                                                                                                \
         const int C = 128 / (R);                                                                                        \
-        return tnx_launch_in_order(delta_scan_kernel<KPT, R>, dim3((dv + C - 1) / C, H, n_requests), dim3(128), 0,      \
-                                   stream, q, k, v, beta, g, state, q_start, q_len, state_slots, out, H, G, dk, dv);    \
+        const dim3 grid((dv + C - 1) / C, H, n_requests);                                                               \
+        if (vec)                                                                                                        \
+            return tnx_launch_in_order(delta_scan_kernel<KPT, R, true>, grid, dim3(128), 0, stream, q, k, v, beta, g,   \
+                                       state, q_start, q_len, state_slots, out, H, G, dk, dv);                          \
+        return tnx_launch_in_order(delta_scan_kernel<KPT, R, false>, grid, dim3(128), 0, stream, q, k, v, beta, g,      \
+                                   state, q_start, q_len, state_slots, out, H, G, dk, dv);                              \
     } while (0)
+    const bool vec = dk % 4 == 0 && !(((uintptr_t)q | (uintptr_t)k | (uintptr_t)g) & 15);
     if (dk <= 16) DSCAN(4, 4);
     if (dk <= 32) DSCAN(4, 8);
     if (dk <= 64) DSCAN(8, 8);
