@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from plain import tutelix_plain as TP
-from tutelix_helpers import CONFIG_A, CONFIG_B, CONFIG_C
+from tutelix_helpers import CONFIG_A, CONFIG_B, CONFIG_C, CONFIGS
 
 
 def _spec(d):
@@ -155,13 +155,13 @@ def test_sizes_the_kernels_do_not_take_are_refused_when_the_model_is_built():
     with pytest.raises(ValueError, match="taps"):
         DecoderModel(_spec(d)[2])
     d = copy.deepcopy(CONFIG_A)
-    d["layers"][1]["mixer"].update(kv_rank=260)
-    with pytest.raises(ValueError, match="256 dims"):
+    d["layers"][1]["mixer"].update(kv_rank=770)
+    with pytest.raises(ValueError, match="768 dims"):
         DecoderModel(_spec(d)[2])
 
 
 def test_all_configurations_build():
-    for d in (CONFIG_A, CONFIG_B, CONFIG_C):
+    for d in CONFIGS.values():
         _, cfg, spec = _spec(d)
         assert len(spec.schedule) == len(cfg.layer_order())
 

@@ -438,6 +438,15 @@ def test_sizes_that_no_fast_path_takes(dtype):
         compare(m, reqs, steps, run_trace_inprocess(m.folder, dtype, steps, 64 * 4), dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rows_wider_than_the_16_bit_attention_kernels_take(dtype):
+    """A latent and heads of more than 256 dims a position run on the CUDA-core attention kernel in either engine."""
+    m = _model("D")
+    reqs = _requests(m, [75, 4, 52], seed=700)
+    for steps in (whole_steps(reqs), mixed_steps(reqs, [9, 2, 31], decode_tail=40)):
+        compare(m, reqs, steps, run_trace_inprocess(m.folder, dtype, steps, 64 * 4), dtype)
+
+
 def test_logits_do_not_depend_on_the_cut_or_the_batch_beyond_rounding():
     m = _model("A")
     reqs = _requests(m, [130, 45], seed=500)

@@ -65,7 +65,13 @@ CONFIG_C = {"architecture": "Tutelix", "vocab": 333, "width": 100, "embedding": 
                 layer("channel_delta", delta(1, 1, 50, 30, 2, 5, 3), None),
                 layer("latent_attention", latent(3, 10, 0, 14, 9, 22, 0.3, 1, 50.0), 70),
                 layer("attention", attention(2, 1, 50, 0.14, 40, 0, 1.0), 44)]}
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
+# Rows wider than the 16-bit attention kernels take (256 dims a position): a latent of 272 with 16 rotated dims, heads of
+# 288 whose values are their keys.
+CONFIG_D = {"architecture": "Tutelix", "vocab": 120, "width": 96, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5},
+            "init_std": 0.1, "layers": [
+                layer("latent_attention", latent(3, 24, 16, 40, 20, 272, 0.2, 37, 300.0), 64),
+                layer("attention", attention(2, 1, 288, 0.06, 50, 32, 1e4), None)]}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
 
 
 class TutelixModel(VononexModel):

@@ -11,9 +11,10 @@
 #include "common.cuh"
 
 namespace {
-constexpr int MAX_DIMS_PER_LANE = 8;   // head_dim <= 256
+constexpr int WIDE_DIMS_PER_LANE = 24;  // head_dim <= 768: rows wider than any 16-bit kernel takes (a wide latent)
 
-template <typename T>
+// MAX_DIMS_PER_LANE: 8 (head_dim <= 256) or WIDE_DIMS_PER_LANE; a lane accumulates that many output dims.
+template <typename T, int MAX_DIMS_PER_LANE>
 __global__ void __launch_bounds__(128)
 attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ cache,
                       const int* __restrict__ block_tables, int bt_stride,
@@ -91,19 +92,21 @@ TNX_EXPORT int tnx_attention_simt(const void* q, int q_stride, const void* cache
                                   int out_stride, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                   int page_size, int window, float scale, int is_h16, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim > 32 * MAX_DIMS_PER_LANE || n_kv_heads <= 0 || n_heads % n_kv_heads)
+    if (head_dim <= 0 || head_dim > 32 * WIDE_DIMS_PER_LANE || n_kv_heads <= 0 || n_heads % n_kv_heads)
         return TNX_ERR_UNSUPPORTED;
     const int warps = 4;
     const long long pairs = (long long)n_tokens * n_heads;
     const int blocks = (int)((pairs + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
-    if (is_h16)
-        return tnx_launch_in_order(attention_simt_kernel<h16>, dim3(blocks), dim3(warps * 32), smem, stream,
-                              (const h16*)q, q_stride, (const h16*)cache, block_tables, bt_stride, token_request,
-                              positions, (h16*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
-                              window, scale);
-    return tnx_launch_in_order(attention_simt_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
-                          (const float*)q, q_stride, (const float*)cache, block_tables, bt_stride, token_request,
-                          positions, (float*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
-                          window, scale);
+#define ASIMT(T, DPL)                                                                                                   \
+    return tnx_launch_in_order(attention_simt_kernel<T, DPL>, dim3(blocks), dim3(warps * 32), smem, stream, (const T*)q,\
+                               q_stride, (const T*)cache, block_tables, bt_stride, token_request, positions, (T*)out,   \
+                               out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size, window, scale)
+    if (head_dim <= 256) {
+        if (is_h16) ASIMT(h16, 8);
+        ASIMT(float, 8);
+    }
+    if (is_h16) ASIMT(h16, WIDE_DIMS_PER_LANE);
+    ASIMT(float, WIDE_DIMS_PER_LANE);
+#undef ASIMT
 }

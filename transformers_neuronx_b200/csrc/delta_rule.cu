@@ -4,8 +4,9 @@
 // so the read-out sees the current token's write.  Query/key heads may be shared by groups of heads (G of them for H
 // heads: head h uses q/k head h / (H / G)).
 //
-// tnx_delta_prep, one thread block per token: from the projections' output (queries, keys and values side by side
-//   from column col0 on: G*dk, G*dk, H*dv channels)
+// tnx_delta_prep, per token (one thread block for a prompt's tokens; several for the few tokens of a decode step, which
+//   share the token's heads and channels, so that eight tokens still fill the device): from the projections' output
+//   (queries, keys and values side by side from column col0 on: G*dk, G*dk, H*dv channels)
 //     y_t[c] = act(sum_j w[j, c] u_(t - taps + 1 + j)[c])        the short causal convolution (zeros before position 0;
 //                                                                 the past comes from this step's rows or from the
 //                                                                 request's state [slots, taps - 1, channels])
@@ -24,6 +25,7 @@
 namespace {
 
 constexpr int PREP_MAX_TAPS = 8;
+constexpr int PREP_FILL_BLOCKS = 2 * 148;   // blocks that fill the device: two an SM
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
@@ -36,7 +38,7 @@ delta_prep_kernel(const T* __restrict__ proj, int ld, int col0, int b_off, const
                   float unit_eps, float q_scale, int act, float* __restrict__ q_out, float* __restrict__ k_out,
                   float* __restrict__ v_out, float* __restrict__ beta_out, float* __restrict__ g_out, int H, int G, int dk,
                   int dv) {
-    extern __shared__ float y[];                      // the token's convolved channels
+    extern __shared__ float y[];                      // a query or key head's convolved channels, per warp
     pdl_launch_dependents();
     pdl_wait();
     const int n = blockIdx.x;
@@ -47,7 +49,7 @@ delta_prep_kernel(const T* __restrict__ proj, int ld, int col0, int b_off, const
     const int keep = taps - 1, nqk = 2 * G * dk, C = nqk + H * dv;
     const T* row = proj + (size_t)n * ld + col0;
     T* st = (keep > 0 && slot >= 0) ? state + (size_t)slot * keep * C : nullptr;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    auto conv = [&](int c) -> float {                 // channel c of this token: convolution, state shift, activation
         float past[PREP_MAX_TAPS];                    // past[b]: the projected value b positions back
         past[0] = to_float(row[c]);
         for (int b = 1; b < taps; ++b) {
@@ -62,22 +64,28 @@ delta_prep_kernel(const T* __restrict__ proj, int ld, int col0, int b_off, const
         for (int j = 0; j < taps; ++j) s = fmaf(conv_w[(size_t)j * C + c], past[taps - 1 - j], s);
         if (alone && st)                              // oldest first: what was one back is now two back
             for (int q = 0; q < keep; ++q) st[(size_t)q * C + c] = from_float<T>(past[keep - 1 - q]);
-        y[c] = apply_activation(s, act);
-    }
-    __syncthreads();
+        return apply_activation(s, act);
+    };
+    // The token's work is spread over gridDim.y blocks: heads of q and k a warp each (unit vectors), the rest a thread
+    // per channel.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int u = warp; u < 2 * G; u += warps) {       // unit vectors: the heads of q, then those of k
-        const float* src = y + u * dk;
+    float* mine = y + warp * dk;
+    for (int u = blockIdx.y * warps + warp; u < 2 * G; u += gridDim.y * warps) {      // the heads of q, then those of k
         float ss = 0.f;
-        for (int i = lane; i < dk; i += 32) ss = fmaf(src[i], src[i], ss);
+        for (int i = lane; i < dk; i += 32) {
+            const float x = conv(u * dk + i);
+            mine[i] = x;
+            ss = fmaf(x, x, ss);
+        }
         const float rinv = (u < G ? q_scale : 1.f) / sqrtf(warp_sum(ss) + unit_eps);
         float* dst = (u < G ? q_out + (size_t)n * G * dk + u * dk : k_out + (size_t)n * G * dk + (u - G) * dk);
-        for (int i = lane; i < dk; i += 32) dst[i] = src[i] * rinv;
+        for (int i = lane; i < dk; i += 32) dst[i] = mine[i] * rinv;      // a lane reads back what it wrote itself
     }
-    for (int c = threadIdx.x; c < H * dv; c += blockDim.x) v_out[(size_t)n * H * dv + c] = y[nqk + c];
-    for (int h = threadIdx.x; h < H; h += blockDim.x)
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
+    for (int c = first; c < H * dv; c += stride) v_out[(size_t)n * H * dv + c] = conv(nqk + c);
+    for (int h = first; h < H; h += stride)
         beta_out[(size_t)n * H + h] = 1.f / (1.f + expf(-to_float(proj[(size_t)n * ld + b_off + h])));
-    for (int c = threadIdx.x; c < H * dk; c += blockDim.x) {
+    for (int c = first; c < H * dk; c += stride) {
         const float rate = expf(a_log[c / dk]);
         g_out[(size_t)n * H * dk + c] = expf(-rate * softplus_f(a[(size_t)n * a_ld + c] + dt_bias[c]));
     }
@@ -211,14 +219,17 @@ TNX_EXPORT int tnx_delta_prep(const void* proj, int ld, int col0, int b_off, con
     if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1 || taps > PREP_MAX_TAPS || !conv_w ||
         (taps > 1 && !state) || act < 0 || act >= TNX_ACT_COUNT)
         return TNX_ERR_BAD_ARG;
-    const size_t smem = (size_t)(2 * G * dk + H * dv) * sizeof(float);
+    const size_t smem = (size_t)8 * dk * sizeof(float);
     if (smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
+    // few tokens: a token's channels over several blocks, so that a step of single tokens fills the device
+    const int most = max(1, max((2 * G + 7) / 8, (H * max(dk, dv) + 255) / 256));
+    const int parts = min(most, max(1, (PREP_FILL_BLOCKS + n_tokens - 1) / n_tokens));
 #define DPREP(T)                                                                                                        \
     do {                                                                                                                \
         if (smem > 48 * 1024)                                                                                           \
             cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-        return tnx_launch_in_order(delta_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, stream, (const T*)proj, ld,   \
-                                   col0, b_off, a, a_ld, conv_w, taps, (T*)state, token_request, positions, q_start,    \
+        return tnx_launch_in_order(delta_prep_kernel<T>, dim3(n_tokens, parts), dim3(256), smem, stream, (const T*)proj,\
+                                   ld, col0, b_off, a, a_ld, conv_w, taps, (T*)state, token_request, positions, q_start,\
                                    q_len, state_slots, a_log, dt_bias, unit_eps, q_scale, act, q_out, k_out, v_out,      \
                                    beta_out, g_out, H, G, dk, dv);                                                      \
     } while (0)

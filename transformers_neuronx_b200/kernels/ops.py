@@ -739,8 +739,8 @@ def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_l
 
 
 def _attention_h16(ctx, group, q, cache, out, n_heads, scale, window, new_kv, chunk=0):
-    if cache.shape[3] != 16 or q.stride(0) % 8 or q.data_ptr() % 16:
-        return False
+    if cache.shape[3] != 16 or cache.shape[4] > 256 or q.stride(0) % 8 or q.data_ptr() % 16:
+        return False                             # rows wider than 256 dims: the CUDA-core kernel takes up to 768
     bt = ctx.block_tables[group]
     fused = None
     if new_kv is not None:

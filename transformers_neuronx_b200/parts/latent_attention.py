@@ -30,6 +30,7 @@ from .registry import register_mixer
 from .rotary import inverse_frequencies
 from .spec import LatentAttentionSpec
 
+MAX_ROW_DIMS = 768               # a position's row: up to 256 dims on the 16-bit attention kernels, beyond that on the CUDA cores
 TENSOR_CORE_TOKENS = 64          # from this many tokens on the per-head products run as one batched tensor-core product
 
 
@@ -46,9 +47,9 @@ class LatentAttention(Mixer):
     def __init__(self, spec: LatentAttentionSpec):
         s = self.spec = spec
         self.pad_dim = -(-(s.kv_rank + s.rot_dim) // 16) * 16
-        if self.pad_dim > 256:
+        if self.pad_dim > MAX_ROW_DIMS:
             raise ValueError(f"a latent of {s.kv_rank} and a rotated part of {s.rot_dim} dims are not supported: the "
-                             "attention kernels take up to 256 dims a position")
+                             f"attention kernels take up to {MAX_ROW_DIMS} dims a position")
         if s.rot_dim % 2 or (s.rot_dim and (s.rotary is None or s.rotary.dims != s.rot_dim)):
             raise ValueError(f"the rotated part of {s.rot_dim} dims needs a rotation over exactly those dims")
         if not (s.scale > 0):

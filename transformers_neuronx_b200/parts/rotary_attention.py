@@ -44,8 +44,8 @@ class RotaryAttention(FusableMixer):
         if s.n_heads % s.n_kv_heads:
             raise ValueError(f"{s.n_heads} heads cannot share {s.n_kv_heads} key/value heads")
         self.pad_dim = -(-max(s.k_dim, s.v_dim) // 16) * 16
-        if self.pad_dim > 256:
-            raise ValueError(f"head sizes {s.k_dim}/{s.v_dim} are not supported: the attention kernels take up to 256")
+        if self.pad_dim > 768:                       # up to 256 on the 16-bit kernels, beyond that on the CUDA cores
+            raise ValueError(f"head sizes {s.k_dim}/{s.v_dim} are not supported: the attention kernels take up to 768")
         if s.rotary is not None and (s.rotary.dims > s.k_dim or s.rotary.dims % 2):
             raise ValueError(f"{s.rotary.dims} rotated dims do not fit heads of {s.k_dim}")
         if s.rotate_values and (s.rotary is None or s.v_dim % 2):
