@@ -160,36 +160,6 @@ __global__ void __launch_bounds__(128) conv_norm_rotate_kernel(const ConvPrep<T>
     }
 }
 
-template <typename T> struct Vec8;
-template <> struct Vec8<h16> {
-    uint4 raw;
-    __device__ __forceinline__ void load(const h16* p) { raw = *(const uint4*)p; }
-    __device__ __forceinline__ void store(h16* p) const { *(uint4*)p = raw; }
-    __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
-    __device__ __forceinline__ void get(float (&v)[8]) const {
-        const h16x2* h = (const h16x2*)&raw;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 f = h16x2_to_float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
-    }
-    __device__ __forceinline__ void set(const float (&v)[8]) {
-        h16x2* h = (h16x2*)&raw;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = floats_to_h16x2(v[2 * i], v[2 * i + 1]);
-    }
-};
-template <> struct Vec8<float> {
-    float4 a, b;
-    __device__ __forceinline__ void load(const float* p) { a = *(const float4*)p; b = *(const float4*)(p + 4); }
-    __device__ __forceinline__ void store(float* p) const { *(float4*)p = a; *(float4*)(p + 4) = b; }
-    __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
-    __device__ __forceinline__ void get(float (&v)[8]) const {
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    }
-    __device__ __forceinline__ void set(const float (&v)[8]) {
-        a = make_float4(v[0], v[1], v[2], v[3]); b = make_float4(v[4], v[5], v[6], v[7]);
-    }
-};
-
 // TAPS: the convolution's taps, 1 when there is none.  grid (tokens, groups of four warps); a warp takes 32 / (dims / 8)
 // heads: first those of queries and keys (which lie side by side in the projection and have one size), then the values'.
 template <typename T, int TAPS>

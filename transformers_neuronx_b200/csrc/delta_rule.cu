@@ -91,6 +91,94 @@ delta_prep_kernel(const T* __restrict__ proj, int ld, int col0, int b_off, const
     }
 }
 
+// The same with eight channels a thread (16-byte loads of the projections and the state, the taps' loads independent of
+// one another): sizes and addresses in multiples of eight channels.
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_prep_vec_kernel(const T* __restrict__ proj, int ld, int col0, int b_off, const float* __restrict__ a, int a_ld,
+                  const float* __restrict__ conv_w, int taps, T* state, const int* __restrict__ token_request,
+                  const int* __restrict__ positions, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                  const int* __restrict__ state_slots, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                  float unit_eps, float q_scale, int act, float* __restrict__ q_out, float* __restrict__ k_out,
+                  float* __restrict__ v_out, float* __restrict__ beta_out, float* __restrict__ g_out, int H, int G, int dk,
+                  int dv) {
+    extern __shared__ float y[];                      // a query or key head's convolved channels, per warp
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int req = token_request[n];
+    if (req < 0) return;                              // a padded row of a captured step
+    const int pos = positions[n], idx = n - q_start[req], slot = state_slots[req];
+    const bool alone = q_len[req] == 1;
+    const int keep = taps - 1, nqk = 2 * G * dk, C = nqk + H * dv;
+    const T* row = proj + (size_t)n * ld + col0;
+    T* st = (keep > 0 && slot >= 0) ? state + (size_t)slot * keep * C : nullptr;
+    auto conv8 = [&](int c, float (&s)[8]) {          // channels c .. c + 7: convolution, state shift, activation
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = 0.f;
+        for (int b = keep; b >= 0; --b) {             // oldest first, as the one-channel form adds them
+            const T* src = row + c;                   // the value b positions back: this step's rows, the state, or zero
+            if (b > 0) {
+                if (pos - b < 0) src = nullptr;
+                else if (idx - b >= 0) src = row + c - (ptrdiff_t)b * ld;
+                else src = st ? st + (size_t)(keep + idx - b) * C + c : nullptr;
+            }
+            Vec8<T> x;
+            if (src) x.load(src); else x.zero();
+            const float* w = conv_w + (size_t)(keep - b) * C + c;
+            const float4 w0 = *(const float4*)w, w1 = *(const float4*)(w + 4);
+            float xv[8];
+            x.get(xv);
+            s[0] = fmaf(w0.x, xv[0], s[0]); s[1] = fmaf(w0.y, xv[1], s[1]); s[2] = fmaf(w0.z, xv[2], s[2]);
+            s[3] = fmaf(w0.w, xv[3], s[3]); s[4] = fmaf(w1.x, xv[4], s[4]); s[5] = fmaf(w1.y, xv[5], s[5]);
+            s[6] = fmaf(w1.z, xv[6], s[6]); s[7] = fmaf(w1.w, xv[7], s[7]);
+            // a request's single row moves its past on: what is b back now is b + 1 back for the next token (the slot
+            // written here was read one round ago)
+            if (alone && st && b < keep) x.store(st + (size_t)(keep - 1 - b) * C + c);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = apply_activation(s[i], act);
+    };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    float* mine = y + warp * dk;
+    for (int u = blockIdx.y * warps + warp; u < 2 * G; u += gridDim.y * warps) {      // the heads of q, then those of k
+        float ss = 0.f;
+        for (int i = 8 * lane; i < dk; i += 256) {
+            float s[8];
+            conv8(u * dk + i, s);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(s[e], s[e], ss);
+            *(float4*)(mine + i) = make_float4(s[0], s[1], s[2], s[3]);
+            *(float4*)(mine + i + 4) = make_float4(s[4], s[5], s[6], s[7]);
+        }
+        const float rinv = (u < G ? q_scale : 1.f) / sqrtf(warp_sum(ss) + unit_eps);
+        float* dst = (u < G ? q_out + (size_t)n * G * dk + u * dk : k_out + (size_t)n * G * dk + (u - G) * dk);
+        for (int i = 8 * lane; i < dk; i += 256) {    // a lane reads back what it wrote itself
+            float4 a0 = *(const float4*)(mine + i), a1 = *(const float4*)(mine + i + 4);
+            a0.x *= rinv; a0.y *= rinv; a0.z *= rinv; a0.w *= rinv; a1.x *= rinv; a1.y *= rinv; a1.z *= rinv; a1.w *= rinv;
+            *(float4*)(dst + i) = a0;
+            *(float4*)(dst + i + 4) = a1;
+        }
+    }
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
+    for (int c = 8 * first; c < H * dv; c += 8 * stride) {
+        float s[8];
+        conv8(nqk + c, s);
+        float* dst = v_out + (size_t)n * H * dv + c;
+        *(float4*)dst = make_float4(s[0], s[1], s[2], s[3]);
+        *(float4*)(dst + 4) = make_float4(s[4], s[5], s[6], s[7]);
+    }
+    for (int h = first; h < H; h += stride)
+        beta_out[(size_t)n * H + h] = 1.f / (1.f + expf(-to_float(proj[(size_t)n * ld + b_off + h])));
+    for (int c = 4 * first; c < H * dk; c += 4 * stride) {          // four channels of one head (dk is a multiple of 8)
+        const float rate = expf(a_log[c / dk]);
+        const float4 x = *(const float4*)(a + (size_t)n * a_ld + c), bias = *(const float4*)(dt_bias + c);
+        *(float4*)(g_out + (size_t)n * H * dk + c) =
+            make_float4(expf(-rate * softplus_f(x.x + bias.x)), expf(-rate * softplus_f(x.y + bias.y)),
+                        expf(-rate * softplus_f(x.z + bias.z)), expf(-rate * softplus_f(x.w + bias.w)));
+    }
+}
+
 // tokens whose inputs are staged in shared memory at a time, in each of two buffers (24 KB of keys, queries and decays)
 __host__ __device__ constexpr int scan_stage(int dkp) { return dkp > 128 ? 4 : dkp > 64 ? 8 : 16; }
 
@@ -224,14 +312,17 @@ TNX_EXPORT int tnx_delta_prep(const void* proj, int ld, int col0, int b_off, con
     // few tokens: a token's channels over several blocks, so that a step of single tokens fills the device
     const int most = max(1, max((2 * G + 7) / 8, (H * max(dk, dv) + 255) / 256));
     const int parts = min(most, max(1, (PREP_FILL_BLOCKS + n_tokens - 1) / n_tokens));
+    const bool vec = dk % 8 == 0 && dv % 8 == 0 && ld % 8 == 0 && col0 % 8 == 0 && a_ld % 4 == 0 &&
+                     !(((uintptr_t)proj | (uintptr_t)state | (uintptr_t)conv_w | (uintptr_t)a | (uintptr_t)dt_bias |
+                        (uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)v_out | (uintptr_t)g_out) & 15);
 #define DPREP(T)                                                                                                        \
     do {                                                                                                                \
-        if (smem > 48 * 1024)                                                                                           \
-            cudaFuncSetAttribute(delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-        return tnx_launch_in_order(delta_prep_kernel<T>, dim3(n_tokens, parts), dim3(256), smem, stream, (const T*)proj,\
-                                   ld, col0, b_off, a, a_ld, conv_w, taps, (T*)state, token_request, positions, q_start,\
-                                   q_len, state_slots, a_log, dt_bias, unit_eps, q_scale, act, q_out, k_out, v_out,      \
-                                   beta_out, g_out, H, G, dk, dv);                                                      \
+        auto kernel = vec ? delta_prep_vec_kernel<T> : delta_prep_kernel<T>;                                            \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        return tnx_launch_in_order(kernel, dim3(n_tokens, parts), dim3(256), smem, stream, (const T*)proj, ld, col0,    \
+                                   b_off, a, a_ld, conv_w, taps, (T*)state, token_request, positions, q_start, q_len,   \
+                                   state_slots, a_log, dt_bias, unit_eps, q_scale, act, q_out, k_out, v_out, beta_out,  \
+                                   g_out, H, G, dk, dv);                                                                \
     } while (0)
     if (is_h16) DPREP(h16);
     DPREP(float);
