@@ -99,8 +99,8 @@ def test_pages_and_state_of_every_run():
     assert [(g.window, g.cache_ids) for g in groups if g.paged] == [(21, [0]), (33, [1, 3, 5]), (None, [7])]
     _, _, spec_b = _spec(CONFIG_B)
     nb = DecoderModel(spec_b).cache_needs()
-    assert nb[1] == PagedKVNeed(1, 80, 64) and nb[4] == PagedKVNeed(1, 128, None)
-    assert nb[(5, 0)] == FixedStateNeed((4, 32, 32), "float32") and (5, 1) not in nb      # one tap keeps no inputs
+    assert nb[1] == PagedKVNeed(1, 64, 64) and nb[4] == PagedKVNeed(1, 128, None)
+    assert nb[(5, 0)] == FixedStateNeed((4, 64, 32), "float32") and (5, 1) not in nb      # one tap keeps no inputs
     _, _, spec_c = _spec(CONFIG_C)
     assert DecoderModel(spec_c).cache_needs()[2] == PagedKVNeed(1, 32, 1)               # no rotated part: the latent alone
 

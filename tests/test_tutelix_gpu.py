@@ -75,7 +75,7 @@ def test_the_norm_behind_a_sublayer_and_the_norm_before_the_next_in_one_kernel(W
 
 
 @pytest.mark.parametrize("rq, rkv, dr, inter, dtype", [
-    (28, 40, 6, True, torch.float32), (80, 64, 16, True, torch.float32), (9, 22, 0, True, torch.float32),
+    (28, 40, 6, True, torch.float32), (72, 48, 16, True, torch.float32), (9, 22, 0, True, torch.float32),
     (48, 96, 32, True, torch.bfloat16), (33, 17, 10, False, torch.float32), (16, 250, 6, True, torch.float32)])
 @pytest.mark.parametrize("col0", [0, 3])
 def test_the_latents_are_normalised_and_the_shared_key_part_is_turned(rq, rkv, dr, inter, dtype, col0):
@@ -106,7 +106,7 @@ def test_the_latents_are_normalised_and_the_shared_key_part_is_turned(rq, rkv, d
 
 
 @pytest.mark.parametrize("H, d, dr, dv, rkv, dtype", [
-    (5, 12, 6, 20, 40, torch.float32), (8, 64, 16, 64, 64, torch.bfloat16), (3, 10, 0, 14, 22, torch.float32),
+    (5, 12, 6, 20, 40, torch.float32), (6, 64, 16, 32, 48, torch.bfloat16), (3, 10, 0, 14, 22, torch.float32),
     (4, 32, 32, 96, 96, torch.bfloat16), (1, 7, 2, 3, 5, torch.float32), (2, 128, 64, 128, 192, torch.float32)])
 @pytest.mark.parametrize("N", [1, 7, 150])
 def test_scores_and_values_through_the_latent_equal_those_of_expanded_heads(H, d, dr, dv, rkv, dtype, N):
@@ -147,7 +147,7 @@ def test_scores_and_values_through_the_latent_equal_those_of_expanded_heads(H, d
     assert float((out[N].float() - 9.0).abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("H, x_head, k, n_out, out_head", [(16, 160, 128, 96, 128), (8, 80, 64, 64, 80), (4, 64, 32, 96, 128),
+@pytest.mark.parametrize("H, x_head, k, n_out, out_head", [(16, 160, 128, 96, 128), (6, 80, 64, 48, 64), (4, 64, 32, 96, 128),
                                                           (3, 128, 96, 128, 128), (2, 256, 192, 40, 48), (1, 64, 64, 8, 8)])
 @pytest.mark.parametrize("N", [64, 150, 300])
 def test_the_per_head_products_of_all_heads_in_one_tensor_core_launch(H, x_head, k, n_out, out_head, N):
@@ -190,7 +190,7 @@ CUTS = [(5, 1), (1, 2), (2, 0), (1, 1), (8, 17), (1, 1), (0, 1), (23, 18)]      
 
 
 @pytest.mark.parametrize("H, G, dk, dv, taps, dtype", [
-    (6, 2, 18, 10, 5, torch.float32), (2, 2, 128, 64, 4, torch.float32), (4, 4, 32, 32, 1, torch.float32),
+    (6, 2, 18, 10, 5, torch.float32), (2, 2, 128, 64, 4, torch.float32), (4, 2, 32, 64, 1, torch.float32),
     (1, 1, 50, 30, 2, torch.float32), (4, 1, 64, 48, 8, torch.bfloat16), (3, 3, 256, 8, 3, torch.float32)])
 @pytest.mark.parametrize("col0", [0, 5])
 def test_what_enters_the_recurrence_across_cuts(H, G, dk, dv, taps, dtype, col0):
@@ -242,7 +242,7 @@ def test_what_enters_the_recurrence_across_cuts(H, G, dk, dv, taps, dtype, col0)
         _close(state[0].float(), u[1, T - keep:].double(), 0.0)
 
 
-@pytest.mark.parametrize("H, G, dk, dv", [(6, 2, 18, 10), (2, 2, 128, 64), (4, 4, 32, 32), (1, 1, 50, 30), (3, 1, 256, 8),
+@pytest.mark.parametrize("H, G, dk, dv", [(6, 2, 18, 10), (2, 2, 128, 64), (4, 2, 32, 64), (1, 1, 50, 30), (3, 1, 256, 8),
                                           (2, 1, 16, 200), (5, 5, 7, 3)])
 def test_the_recurrence_across_cuts_and_slots(H, G, dk, dv):
     """The scan over two requests cut as above, against the plain recurrence over the whole sequences; then a third

@@ -47,15 +47,15 @@ CONFIG_A = {"architecture": "Tutelix", "vocab": 211, "width": 72, "embedding": {
                 layer("latent_attention", latent(5, 12, 6, 20, 28, 40, 0.25, 33, 77.0), None),
                 layer("channel_delta", delta(6, 2, 18, 10, 5, 7, 12), 50),
                 layer("attention", attention(2, 1, 64, 0.125, None, 64, 10000.0), None)]}
-# Sizes the tensor-core kernels take: head sizes 128 and 64, latents of 64 + 16 and 96 + 32 dims a position, windows of
+# Sizes the tensor-core kernels take: head sizes 128 and 64, latents of 48 + 16 and 96 + 32 dims a position, windows of
 # 64 and 48, a layer without mask, recurrences with 128 and 32 rows a column, a single looped layer, one tap.
 CONFIG_B = {"architecture": "Tutelix", "vocab": 1003, "width": 256, "embedding": {"scale": 16.0}, "norm": {"eps": 1e-6},
             "init_std": 0.1, "loop": {"start": 2, "stop": 3, "times": 2}, "layers": [
                 layer("channel_delta", delta(2, 2, 128, 64, 4, 16, 24), 320),
-                layer("latent_attention", latent(8, 64, 16, 64, 80, 64, 0.11, 64, 50000.0), 128),
-                layer("attention", attention(4, 2, 128, 0.09, 48, 64, 500000.0), 384),
+                layer("latent_attention", latent(6, 64, 16, 32, 72, 48, 0.11, 64, 20000.0), 128),
+                layer("attention", attention(6, 3, 128, 0.09, 48, 32, 100000.0), 384),
                 layer("latent_attention", latent(4, 32, 32, 96, 48, 96, 0.12, None, 3e4), None),
-                layer("channel_delta", delta(4, 4, 32, 32, 1, 8, 8), 192)]}
+                layer("channel_delta", delta(4, 2, 32, 64, 1, 8, 8), 192)]}
 # A width and a vocabulary that are no multiples of 8 (the 16-bit engine falls back to the CUDA-core product and to
 # scalar loads), as many key heads as heads, head sizes of 20, no loop, a window of one page and a window of a single
 # position, an unrotated attention layer, a latent without rotated part, a recurrence of one head.
