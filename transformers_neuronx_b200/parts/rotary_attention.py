@@ -97,9 +97,13 @@ class RotaryAttention(FusableMixer):
                             s.rotary.dims if s.rotary is not None else 0, self.inv_freq_v, q, k, v, H, G, s.k_dim,
                             s.v_dim, D)
         cache, g = ctx.cache(sub), ctx.cache_group(sub)
-        att = ctx.scratch(N, H * D)
+        # heads that are neither padded, turned back nor scaled go from the attention kernel straight to their place
+        direct = (D == s.v_dim and self.inv_freq_v is None and out_scale == 1.0 and inner_out.dtype == q.dtype
+                  and inner_out.stride(0) % 8 == 0 and inner_out.data_ptr() % 16 == 0)
+        att = inner_out if direct else ctx.scratch(N, H * D)
         ops.attention(ctx, g, q, cache, att, H, s.scale, s.window or 0, new_kv=(k, v, ctx.slot_mapping[g]))
-        ops.rotary_unrotate(att, ctx.token_request, ctx.positions, self.inv_freq_v, out_scale, inner_out, H, s.v_dim, D)
+        if not direct:
+            ops.rotary_unrotate(att, ctx.token_request, ctx.positions, self.inv_freq_v, out_scale, inner_out, H, s.v_dim, D)
 
 
 register_mixer("rotary_attention", RotaryAttention)
