@@ -45,6 +45,15 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, float x_scale, cons
     }
 }
 
+// Four neighbouring elements stored at once (8 bytes of 16-bit numbers, 16 of floats).
+__device__ __forceinline__ void store4(float* p, const float4& v) { *(float4*)p = v; }
+__device__ __forceinline__ void store4(h16* p, const float4& v) {
+    uint2 raw;
+    *(h16x2*)&raw.x = floats_to_h16x2(v.x, v.y);
+    *(h16x2*)&raw.y = floats_to_h16x2(v.z, v.w);
+    *(uint2*)p = raw;
+}
+
 // The norm on a sublayer's output only:  out = x + add_scale * (delta / sqrt(mean(delta^2) + eps) * (w + w_offset)).
 // x is the 32-bit residual stream (out_f32 may be x itself), delta what the sublayer produced.
 // then_norm: out_act receives a further RMS norm of the new row, out / sqrt(mean(out^2) + then_eps) * (w_then + then_offset),
@@ -54,25 +63,58 @@ __global__ void rms_norm_add_kernel(const float* x, float add_scale, const float
                                     const float* __restrict__ w, float w_offset, float eps, float* out_f32,
                                     TA* __restrict__ out_act, int H, int then_norm, const float* __restrict__ w_then,
                                     float then_offset, float then_eps) {
-    extern __shared__ __align__(16) float row[];
+    extern __shared__ __align__(16) float row[];      // the sublayer's row; with VEC the stream's row behind it
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const size_t src = (size_t)blockIdx.x * H;
     float s = 0.f;
     if (VEC) {
+        // sixteen bytes an access throughout, and the stream's row fetched along with the sublayer's, so that nothing
+        // is waited for behind the first sum
         const float4* ds = (const float4*)(delta + src);
+        const float4* xs = (const float4*)(x + src);
+        float4* rd = (float4*)row;
+        float4* rx = (float4*)(row + H);
         for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
             const float4 v = ds[c];
-            ((float4*)row)[c] = v;
+            rd[c] = v;
+            rx[c] = xs[c];
             s += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
         }
-    } else {
-        for (int c = threadIdx.x; c < H; c += blockDim.x) {
-            const float v = delta[src + c];
-            row[c] = v;
-            s += v * v;
+        const float rinv = 1.0f / sqrtf(block_sum(s, scratch) / (float)H + eps);
+        float s2 = 0.f;
+        for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
+            float4 y = rd[c];
+            const float4 xv = rx[c];
+            y.x *= rinv; y.y *= rinv; y.z *= rinv; y.w *= rinv;
+            if (w) {
+                const float4 g = ((const float4*)w)[c];
+                y.x *= g.x + w_offset; y.y *= g.y + w_offset; y.z *= g.z + w_offset; y.w *= g.w + w_offset;
+            }
+            y.x = fmaf(add_scale, y.x, xv.x); y.y = fmaf(add_scale, y.y, xv.y);
+            y.z = fmaf(add_scale, y.z, xv.z); y.w = fmaf(add_scale, y.w, xv.w);
+            if (out_f32) ((float4*)(out_f32 + src))[c] = y;
+            if (then_norm) { rd[c] = y; s2 += (y.x * y.x + y.y * y.y) + (y.z * y.z + y.w * y.w); }
+            else if (out_act) store4(out_act + src + 4 * c, y);
         }
+        if (!then_norm || !out_act) return;
+        const float rinv2 = 1.0f / sqrtf(block_sum(s2, scratch) / (float)H + then_eps);  // each thread reads back its own columns
+        for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
+            float4 y = rd[c];
+            y.x *= rinv2; y.y *= rinv2; y.z *= rinv2; y.w *= rinv2;
+            if (w_then) {
+                const float4 g = ((const float4*)w_then)[c];
+                y.x *= g.x + then_offset; y.y *= g.y + then_offset; y.z *= g.z + then_offset; y.w *= g.w + then_offset;
+            }
+            store4(out_act + src + 4 * c, y);
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = delta[src + c];
+        row[c] = v;
+        s += v * v;
     }
     const float ms = block_sum(s, scratch) / (float)H;
     const float rinv = 1.0f / sqrtf(ms + eps);
@@ -99,9 +141,12 @@ TNX_EXPORT int tnx_rms_norm_add(const float* x, float add_scale, const float* de
                                 int then_norm, const float* w_then, float then_offset, float then_eps,
                                 cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    const size_t smem = (size_t)H * sizeof(float);
-    if (H <= 0 || smem > 200 * 1024 || !x || !delta) return TNX_ERR_UNSUPPORTED;
-    const bool vec = H % 4 == 0 && ((uintptr_t)delta % 16) == 0;
+    if (H <= 0 || !x || !delta) return TNX_ERR_UNSUPPORTED;
+    const bool vec = H % 4 == 0 && (size_t)2 * H * sizeof(float) <= 200 * 1024 &&
+                     !(((uintptr_t)delta | (uintptr_t)x | (uintptr_t)out_f32 | (uintptr_t)out_act | (uintptr_t)w |
+                        (uintptr_t)w_then) & 15);
+    const size_t smem = (size_t)(vec ? 2 : 1) * H * sizeof(float);
+    if (smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
 #define RMS_LAUNCH(TA, V)                                                                                              \
     do {                                                                                                               \
