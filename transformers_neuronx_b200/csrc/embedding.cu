@@ -1,6 +1,8 @@
-// Token embedding gather + learned position embedding.
+// Token embedding gather + learned or sinusoidal position embedding.
 //
 //   x[n, :] = tok_scale * (tok_table ? tok_table[ids[n], :] : pre[n, :]) + (pos_table ? pos_table[positions[n] + offset, :] : 0)
+//             + (sin_freq ? s(positions[n]) : 0),   s(p)[2i] = sin(p sin_freq[i]), s(p)[2i + 1] = cos(p sin_freq[i])
+//   (the angle is the 32-bit product of the position and the 32-bit frequency; sinf and cosf, not the fast intrinsics)
 //
 // written as the 32-bit residual stream and, when asked, also in the activation type for a block
 // that reads its input un-normalised.  `pre` is the 32-bit output of project_in when the embedding
@@ -12,15 +14,18 @@ template <typename TT, typename TA>
 __global__ void embed_kernel(const TT* __restrict__ tok_table, const float* __restrict__ pre,
                              const int* __restrict__ ids, const TT* __restrict__ pos_table,
                              const int* __restrict__ positions, int pos_offset, float tok_scale,
-                             float* __restrict__ out_f32, TA* __restrict__ out_act, int H) {
+                             const float* __restrict__ sin_freq, float* __restrict__ out_f32, TA* __restrict__ out_act,
+                             int H) {
     pdl_launch_dependents();
     pdl_wait();
     const int n = blockIdx.x;
     const TT* trow = tok_table ? tok_table + (size_t)ids[n] * H : nullptr;
     const TT* prow = pos_table ? pos_table + (size_t)(positions[n] + pos_offset) * H : nullptr;
+    const float pos = sin_freq ? (float)positions[n] : 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = (trow ? to_float(trow[c]) : pre[(size_t)n * H + c]) * tok_scale;
         if (prow) v += to_float(prow[c]);
+        if (sin_freq) { const float a = pos * sin_freq[c >> 1]; v += (c & 1) ? cosf(a) : sinf(a); }
         if (out_f32) out_f32[(size_t)n * H + c] = v;
         if (out_act) out_act[(size_t)n * H + c] = from_float<TA>(v);
     }
@@ -53,14 +58,14 @@ TNX_EXPORT int tnx_patch_tokens(int* tokens, const int* src, const int* sampled,
 
 // table_h16 / act_h16: 1 when the tables / the activation output are bfloat16, 0 for float.
 TNX_EXPORT int tnx_embed(const void* tok_table, const float* pre, const int* ids, const void* pos_table,
-                         const int* positions, int pos_offset, float tok_scale, float* out_f32, void* out_act,
-                         int N, int H, int table_h16, int act_h16, cudaStream_t stream) {
+                         const int* positions, int pos_offset, float tok_scale, const float* sin_freq, float* out_f32,
+                         void* out_act, int N, int H, int table_h16, int act_h16, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (H <= 0 || (!tok_table && !pre)) return TNX_ERR_BAD_ARG;
     const int threads = H >= 1024 ? 256 : 128;
 #define LAUNCH(TT, TA)                                                                                        \
     tnx_launch_in_order(embed_kernel<TT, TA>, dim3(N), dim3(threads), 0, stream, (const TT*)tok_table, pre, ids,   \
-                   (const TT*)pos_table, positions, pos_offset, tok_scale, out_f32, (TA*)out_act, H)
+                   (const TT*)pos_table, positions, pos_offset, tok_scale, sin_freq, out_f32, (TA*)out_act, H)
     if (table_h16 && act_h16) return LAUNCH(h16, h16);
     if (table_h16 && !act_h16) return LAUNCH(h16, float);
     if (!table_h16 && act_h16) return LAUNCH(float, h16);

@@ -6,6 +6,10 @@
 //   expert e on input x:  g = W_gate x, u = W_up x (both clamped where the part gives limits),
 //                         y = g * sigmoid(alpha g) * (u + up_shift),  result W_down y
 //   out = sum_j expert_{e_j}(w_j h)   (weight on the input)    or    sum_j w_j expert_{e_j}(h)   (on the output)
+//   an expert without a gate (form 1):  y = relu(W_up x)^2,  result W_down y
+//   routing options (sigmoid scores): a correction per expert added to the scores for the CHOICE only; experts in equal
+//   groups of neighbours, a group scored by the sum of its group_top largest choice scores, only the keep_groups best
+//   groups' experts open to the choice; weights w_j / (sum_j w_j + renorm_eps) * weight_scale
 //
 // Kernels of this file (T: the activations' type, TW: the stored type of the experts' matrices):
 //   moe_router_kernel      a block a token: logits, scores, the top experts and their weights
@@ -70,14 +74,22 @@ __device__ __forceinline__ float warp_dot(const TW* __restrict__ w, const float*
     return warp_sum(s);
 }
 
+struct RouterOptions {
+    const float* correction;     // [E] or null
+    int n_groups, keep_groups, group_top;
+    float renorm_eps, weight_scale;
+};
+
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
 moe_router_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ wr, const int* __restrict__ token_request,
                   int* __restrict__ ids, float* __restrict__ weights, int W, int E, int top, int softmax_scores,
-                  int renormalize) {
-    extern __shared__ __align__(16) float sm[];            // [W] the row, [E] the scores
+                  int renormalize, RouterOptions ro) {
+    extern __shared__ __align__(16) float sm[];            // [W] the row, [E] the logits (or choice scores), [E] the scores, [E] groups
     float* x = sm;
     float* z = sm + ((W + 3) & ~3);
+    float* sc = z + E;
+    float* gscore = sc + E;
     pdl_launch_dependents();
     pdl_wait();
     const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -95,7 +107,57 @@ moe_router_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ wr, co
     __syncthreads();
     if (warp != 0) return;
     // The choice is made on the logits: both scores grow with them, and a sigmoid that has run out of bits near 1
-    // would tie experts that their logits still tell apart.
+    // would tie experts that their logits still tell apart.  With a correction or groups the choice is made on
+    // choice score = sigmoid + correction, as the design says, and the weight is the uncorrected sigmoid.
+    const bool corrected = ro.correction != nullptr || ro.n_groups > 1;
+    if (corrected) {
+        for (int e = lane; e < E; e += 32) {
+            const float s0 = 1.f / (1.f + expf(-z[e]));
+            sc[e] = s0;
+            z[e] = s0 + (ro.correction ? ro.correction[e] : 0.f);
+        }
+        __syncwarp();
+        if (ro.n_groups > 1) {
+            const int size = E / ro.n_groups;
+            for (int g = lane; g < ro.n_groups; g += 32) {          // the sum of the group's largest choice scores
+                float total = 0.f;
+                unsigned long long taken = 0ull;                     // group_top is small: a pass per pick
+                for (int j = 0; j < ro.group_top && j < size; ++j) {
+                    float best = -INFINITY;
+                    int arg = -1;
+                    for (int i = 0; i < size; ++i) {
+                        if (i < 64 && (taken >> i & 1ull)) continue;
+                        const float v = z[g * size + i];
+                        if (arg < 0 || v > best) { best = v; arg = i; }
+                    }
+                    if (arg >= 0 && arg < 64) taken |= 1ull << arg;
+                    total += best;
+                }
+                gscore[g] = total;
+            }
+            __syncwarp();
+            // the keep_groups best groups stay (of equal ones the lowest index); the others' experts cannot be chosen
+            for (int j = 0; j < ro.keep_groups; ++j) {
+                float best = -INFINITY;
+                int arg = 0x7fffffff;
+                for (int g = lane; g < ro.n_groups; g += 32) {
+                    const float v = gscore[g];
+                    if (v == v && (v > best || arg == 0x7fffffff) && v != INFINITY) { best = v; arg = g; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                    if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+                }
+                if (lane == 0 && arg != 0x7fffffff) gscore[arg] = INFINITY;      // kept
+                __syncwarp();
+            }
+            for (int e = lane; e < E; e += 32)
+                if (gscore[e / size] != INFINITY) z[e] = -INFINITY;
+            __syncwarp();
+        }
+    }
     float mx = -INFINITY, sum = 0.f;
     if (softmax_scores) {
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
@@ -120,7 +182,7 @@ moe_router_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ wr, co
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
         chosen[j] = arg;
-        chosen_w[j] = softmax_scores ? expf(best - mx) / sum : 1.f / (1.f + expf(-best));
+        chosen_w[j] = corrected ? sc[arg] : (softmax_scores ? expf(best - mx) / sum : 1.f / (1.f + expf(-best)));
         total += chosen_w[j];
         if (lane == 0) z[arg] = -INFINITY;
         __syncwarp();
@@ -128,7 +190,7 @@ moe_router_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ wr, co
     if (lane == 0)
         for (int j = 0; j < top; ++j) {
             ids[(size_t)n * top + j] = chosen[j];
-            weights[(size_t)n * top + j] = renormalize ? chosen_w[j] / total : chosen_w[j];
+            weights[(size_t)n * top + j] = (renormalize ? chosen_w[j] / (total + ro.renorm_eps) : chosen_w[j]) * ro.weight_scale;
         }
 }
 
@@ -136,9 +198,11 @@ struct ExpertMath {
     float gate_max, up_min, up_max;     // clamps (infinite: none)
     float alpha, up_shift;              // y = g * sigmoid(alpha g) * (u + up_shift)
     int weight_on_input;
+    int form;                           // 0: gated as above;  1: no gate, y = relu(u)^2
 };
 
 __device__ __forceinline__ float expert_act(float g, float u, const ExpertMath& m) {
+    if (m.form == 1) { const float r = fmaxf(g, 0.f); return r * r; }      // without a gate the one product arrives as g
     g = fminf(g, m.gate_max);
     u = fminf(fmaxf(u, m.up_min), m.up_max);
     return g / (1.f + expf(-m.alpha * g)) * (u + m.up_shift);
@@ -272,7 +336,8 @@ moe_gate_up_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ gate_
     const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int count = pairs_of_expert(ids, n_pairs, e, list, &count_s);
     if (count == 0) return;
-    const TW* wg = gate_up + (size_t)e * 2 * F * W;
+    const bool gated = m.form == 0;                      // without a gate: [E, F, W], the up rows alone
+    const TW* wg = gate_up + (size_t)e * (gated ? 2 : 1) * F * W;
     const TW* wu = wg + (size_t)F * W;
     const bool vec = W % 8 == 0 && ((uintptr_t)gate_up % 16) == 0;
     const int f_end = min(F, (blockIdx.y + 1) * per_block);
@@ -298,7 +363,8 @@ moe_gate_up_kernel(const T* __restrict__ h, int ld, const TW* __restrict__ gate_
         __syncthreads();
         for (int f = blockIdx.y * per_block + warp; f < f_end; f += 4) {
             float g[MT], u[MT];
-            rows_dot<T, TW, true>(wg + (size_t)f * W, wu + (size_t)f * W, xs, W, rows, lane, vec, g, u);
+            if (gated) rows_dot<T, TW, true>(wg + (size_t)f * W, wu + (size_t)f * W, xs, W, rows, lane, vec, g, u);
+            else rows_dot<T, TW, false>(wg + (size_t)f * W, nullptr, xs, W, rows, lane, vec, g, u);
 #pragma unroll
             for (int r = 0; r < MT; ++r)
                 if (r < rows && lane == r) y[(size_t)list[c0 + r] * F + f] = from_float<T>(expert_act(g[r], u[r], m));
@@ -364,16 +430,22 @@ moe_sum_kernel(const float* __restrict__ per_pair, const int* __restrict__ ids, 
 
 TNX_EXPORT int tnx_moe_route(const void* h, int ld, const void* router, const int* token_request, int* ids, float* weights,
                              int N, int W, int E, int top, int softmax_scores, int renormalize, int h_h16, int w_h16,
-                             cudaStream_t stream) {
+                             const float* correction, int n_groups, int keep_groups, int group_top, float renorm_eps,
+                             float weight_scale, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (W <= 0 || E <= 0 || E > MAX_EXPERTS || top <= 0 || top > MAX_TOP || top > E) return TNX_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(((W + 3) & ~3) + E) * sizeof(float);
+    if (n_groups < 1 || E % n_groups || keep_groups < 1 || keep_groups > n_groups || group_top < 1 ||
+        (long long)keep_groups * (E / n_groups) < top || ((correction || n_groups > 1) && softmax_scores))
+        return TNX_ERR_BAD_ARG;
+    if (n_groups > 1 && E / n_groups > 64 && group_top > 1) return TNX_ERR_UNSUPPORTED;
+    const RouterOptions ro{correction, n_groups, keep_groups, group_top, renorm_eps, weight_scale};
+    const size_t smem = (size_t)(((W + 3) & ~3) + 3 * E) * sizeof(float);
     if (smem > 160 * 1024) return TNX_ERR_UNSUPPORTED;
 #define GO(T, TW)                                                                                                       \
     do {                                                                                                                \
         if (smem > 48 * 1024) cudaFuncSetAttribute(moe_router_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         return tnx_launch_in_order(moe_router_kernel<T, TW>, dim3(N), dim3(128), smem, stream, (const T*)h, ld,         \
-                                   (const TW*)router, token_request, ids, weights, W, E, top, softmax_scores, renormalize); \
+                                   (const TW*)router, token_request, ids, weights, W, E, top, softmax_scores, renormalize, ro); \
     } while (0)
     if (h_h16 && w_h16) GO(h16, h16);
     if (h_h16) GO(h16, float);
@@ -385,15 +457,16 @@ TNX_EXPORT int tnx_moe_route(const void* h, int ld, const void* router, const in
 TNX_EXPORT int tnx_moe_experts(const void* h, int ld, const void* gate_up, const void* down, const int* ids,
                                const float* weights, void* y, float* per_pair, float* out, int N, int W, int F, int top,
                                int n_experts, float gate_max, float up_min, float up_max, float alpha, float up_shift,
-                               int weight_on_input, int accumulate, int h_h16, int w_h16, cudaStream_t stream) {
+                               int weight_on_input, int accumulate, int h_h16, int w_h16, int form, cudaStream_t stream) {
+    // form 0: gate_up is [E, 2F, W] (gated experts); form 1: [E, F, W] (the up rows alone, y = relu(u)^2)
     if (N <= 0) return 0;
-    if (W <= 0 || F <= 0 || top <= 0 || top > MAX_TOP || n_experts <= 0) return TNX_ERR_UNSUPPORTED;
+    if (W <= 0 || F <= 0 || top <= 0 || top > MAX_TOP || n_experts <= 0 || form < 0 || form > 1) return TNX_ERR_UNSUPPORTED;
     const int pairs = N * top;
     const size_t el = h_h16 ? 2 : 4;
     const size_t smem1 = (((size_t)MT * W * el + 15) & ~(size_t)15) + (size_t)pairs * sizeof(int);
     const size_t smem2 = (((size_t)MT * F * el + 15) & ~(size_t)15) + (size_t)pairs * sizeof(int);
     if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return TNX_ERR_UNSUPPORTED;
-    ExpertMath m{gate_max, up_min, up_max, alpha, up_shift, weight_on_input};
+    ExpertMath m{gate_max, up_min, up_max, alpha, up_shift, weight_on_input, form};
     // slices that give every SM a few blocks of the experts that are chosen
     const int busy = n_experts < pairs ? n_experts : pairs;
     int per1 = 4; while (per1 < F && (long long)busy * ((F + per1 - 1) / per1) > 1024) per1 *= 2;

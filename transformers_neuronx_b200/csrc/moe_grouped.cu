@@ -8,6 +8,7 @@
 //                        gets depends on the order in which threads arrive; a row's result does not depend on where it sits
 //   moe_gather_kernel    x[row(pair)] = weight * h[token]  (or h[token] when the weight multiplies the output), 16-bit
 //   moe_act_kernel       y = g * sigmoid(alpha g) * (u + up_shift), g and u clamped, from the gate/up product's output
+//                        (moe_act_relu2_kernel: y = relu(u)^2 for experts without a gate)
 //   moe_combine_kernel   out[token] (+)= sum over the token's pairs, in the order of the choice, of the down product's rows
 //
 // Nothing is read on the host: the sizes of the buffers follow from the numbers of tokens and experts alone (at most
@@ -99,6 +100,29 @@ moe_act_kernel(const h16* __restrict__ gu, h16* __restrict__ y, const int* __res
     }
 }
 
+// Experts without a gate: y = relu(u)^2 from the up product's output [rows, F].
+__global__ void __launch_bounds__(256)
+moe_act_relu2_kernel(const h16* __restrict__ u, h16* __restrict__ y, const int* __restrict__ group_of_tile, int TILE, int F) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    if (group_of_tile[row / TILE] < 0) return;
+    const h16* src = u + (size_t)row * F;
+    h16* dst = y + (size_t)row * F;
+    if (F % 2 == 0) {
+        for (int c = threadIdx.x * 2; c < F; c += blockDim.x * 2) {
+            const float2 f = h16x2_to_float2(*(const h16x2*)(src + c));
+            const float a = fmaxf(f.x, 0.f), b = fmaxf(f.y, 0.f);
+            *(h16x2*)(dst + c) = floats_to_h16x2(a * a, b * b);
+        }
+    } else {
+        for (int c = threadIdx.x; c < F; c += blockDim.x) {
+            const float a = fmaxf(h16_to_float(src[c]), 0.f);
+            dst[c] = float_to_h16(a * a);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ row_of_pair, const float* __restrict__ weights,
                    float* out, int W, int top, int accumulate, int weight_on_input) {
@@ -140,8 +164,11 @@ TNX_EXPORT int tnx_moe_gather(const void* h, int ld, const float* weights, const
 }
 
 TNX_EXPORT int tnx_moe_act(const void* gu, void* y, const int* group_of_tile, int tile, int rows, int F, float gate_max,
-                           float up_min, float up_max, float alpha, float up_shift, cudaStream_t stream) {
+                           float up_min, float up_max, float alpha, float up_shift, int form, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (form == 1)
+        return tnx_launch_in_order(moe_act_relu2_kernel, dim3(rows), dim3(F >= 512 ? 256 : 128), 0, stream, (const h16*)gu,
+                                   (h16*)y, group_of_tile, tile, F);
     return tnx_launch_in_order(moe_act_kernel, dim3(rows), dim3(F >= 512 ? 256 : 128), 0, stream, (const h16*)gu, (h16*)y,
                                group_of_tile, tile, F, gate_max, up_min, up_max, alpha, up_shift);
 }

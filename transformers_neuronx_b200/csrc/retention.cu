@@ -69,6 +69,17 @@ __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+// What may change from token to token (a selective state-space recurrence): S_t = decay_t S_(t-1) + kscale_t k_t v_t^T with
+// decay [tokens, H] and kscale [tokens, H] (each absent: the head's fixed decay, 1), and queries and keys that the heads
+// of a group share: qk_heads of them for H heads, head h reading those of h / (H / qk_heads).  A stage carries its
+// tokens' two numbers behind its values.
+struct TokenGates {
+    const float* decay;
+    const float* kscale;
+    int qk_heads;
+};
+__host__ __device__ __forceinline__ int token_gate_floats(int stage_tokens) { return (2 * stage_tokens + 3) & ~3; }
+
 // KPT: rows of a column one thread keeps; R: lanes a column's rows are spread over (KPT * R >= k_dim).
 // VEC: k_dim is a multiple of four: a thread's rows come in runs of four (rows 4 (r + R m) .. + 3), read as one
 // 16-byte piece, and the stages are filled with 16-byte asynchronous copies; otherwise with plain loads.
@@ -84,7 +95,7 @@ __global__ void __launch_bounds__(128)
 retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v, int v_ld,
                       const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ q_start,
                       const int* __restrict__ q_len, const int* __restrict__ state_slots, float* __restrict__ out,
-                      int H, int dk, int dv, int C, int stage_tokens) {
+                      int H, int dk, int dv, int C, int stage_tokens, TokenGates tg) {
     constexpr int DKP = KPT * R;
     const int SCAN_TOKENS = stage_tokens;
     extern __shared__ __align__(16) float sm[];
@@ -96,12 +107,13 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
     const int slot = state_slots[req];
     if (slot < 0) return;
     const int t_first = q_start[req];
-    const int stage_floats = SCAN_TOKENS * (2 * DKP + C);
+    const int stage_floats = SCAN_TOKENS * (2 * DKP + C) + token_gate_floats(SCAN_TOKENS);
     float* part = sm + SCAN_STAGES * stage_floats;    // [SCAN_TOKENS][C * R] partial sums of the stage being computed
     const int jl = threadIdx.x / R, r = threadIdx.x % R;
     const int j = blockIdx.x * C + jl;
     const bool col = j < dv;
-    const float dec = decay[h];
+    const float dec_fixed = decay ? decay[h] : 1.f;
+    const int Hq = tg.qk_heads, hq = h / (H / Hq);
     float* st = state + (((size_t)slot * H + h) * dv + (col ? j : 0)) * dk;
 
     // Fills stage `s` with the tokens from t0 on: queries and keys by asynchronous copies (VEC) or plain loads,
@@ -111,20 +123,26 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
         float* ks = qs + SCAN_TOKENS * DKP;
         float* vs = ks + SCAN_TOKENS * DKP;
         const int nt = min(SCAN_TOKENS, len - t0);
-        const size_t g0 = (size_t)(t_first + t0) * H * dk + (size_t)h * dk;
+        const size_t g0 = (size_t)(t_first + t0) * Hq * dk + (size_t)hq * dk;
         if (VEC) {
             const int pieces = dk / 4;
             for (int e = threadIdx.x; e < nt * pieces; e += blockDim.x) {
                 const int tt = e / pieces, c = e % pieces;
-                cp_async_16(qs + tt * DKP + 4 * c, qr + g0 + (size_t)tt * H * dk + 4 * c);
-                cp_async_16(ks + tt * DKP + 4 * c, kr + g0 + (size_t)tt * H * dk + 4 * c);
+                cp_async_16(qs + tt * DKP + 4 * c, qr + g0 + (size_t)tt * Hq * dk + 4 * c);
+                cp_async_16(ks + tt * DKP + 4 * c, kr + g0 + (size_t)tt * Hq * dk + 4 * c);
             }
         } else {
             for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) {
                 const int tt = e / dk, i = e % dk;
-                qs[tt * DKP + i] = qr[g0 + (size_t)tt * H * dk + i];
-                ks[tt * DKP + i] = kr[g0 + (size_t)tt * H * dk + i];
+                qs[tt * DKP + i] = qr[g0 + (size_t)tt * Hq * dk + i];
+                ks[tt * DKP + i] = kr[g0 + (size_t)tt * Hq * dk + i];
             }
+        }
+        float* gs = vs + SCAN_TOKENS * C;              // [decay of the stage's tokens][their key scales]
+        for (int e = threadIdx.x; e < nt; e += blockDim.x) {
+            const size_t at = (size_t)(t_first + t0 + e) * H + h;
+            gs[e] = tg.decay ? tg.decay[at] : dec_fixed;
+            gs[SCAN_TOKENS + e] = tg.kscale ? tg.kscale[at] : 1.f;
         }
         if (VASYNC) {
             constexpr int PER = 16 / sizeof(T);       // values in a 16-byte piece
@@ -175,9 +193,11 @@ retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr
         const float* qs = sm + stage * stage_floats;
         const float* ks = qs + SCAN_TOKENS * DKP;
         const float* vs = ks + SCAN_TOKENS * DKP;
+        const float* gs = vs + SCAN_TOKENS * C;
 #pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = VASYNC ? to_float(((const T*)vs)[tt * C + jl]) : vs[tt * C + jl];
+            const float dec = gs[tt];
+            const float vj = (VASYNC ? to_float(((const T*)vs)[tt * C + jl]) : vs[tt * C + jl]) * gs[SCAN_TOKENS + tt];
             const float* kt = ks + tt * DKP;
             const float* qt = qs + tt * DKP;
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
@@ -235,7 +255,7 @@ __global__ void __launch_bounds__(128)
 retention_scan4_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v, int v_ld,
                        const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ q_start,
                        const int* __restrict__ q_len, const int* __restrict__ state_slots, float* __restrict__ out,
-                       int H, int dk, int dv, int C, int stage_tokens) {
+                       int H, int dk, int dv, int C, int stage_tokens, TokenGates tg) {
     constexpr int DKP = KPT * R;
     constexpr int GROUP = 4 * R + 4;                 // floats of one (token, column group) in `part`
     const int ST = stage_tokens, CG = C / 4;
@@ -248,11 +268,12 @@ retention_scan4_kernel(const float* __restrict__ qr, const float* __restrict__ k
     const int slot = state_slots[req];
     if (slot < 0) return;
     const int t_first = q_start[req];
-    const int stage_floats = ST * (2 * DKP + C);
+    const int stage_floats = ST * (2 * DKP + C) + token_gate_floats(ST);
     float* part = sm + SCAN_STAGES * stage_floats;   // [ST][CG][GROUP]
     const int g = threadIdx.x / R, r = threadIdx.x % R;
     const int j0 = blockIdx.x * C + 4 * g;
-    const float dec = decay[h];
+    const float dec_fixed = decay ? decay[h] : 1.f;
+    const int Hq = tg.qk_heads, hq = h / (H / Hq);
     float* st = state + (((size_t)slot * H + h) * dv) * dk;
 
     auto fill = [&](int s, int t0) {
@@ -260,14 +281,20 @@ retention_scan4_kernel(const float* __restrict__ qr, const float* __restrict__ k
         float* ks = qs + ST * DKP;
         float* vs = ks + ST * DKP;
         const int nt = min(ST, len - t0);
-        const size_t g0 = (size_t)(t_first + t0) * H * dk + (size_t)h * dk;
+        const size_t g0 = (size_t)(t_first + t0) * Hq * dk + (size_t)hq * dk;
         const int pieces = dk / 4;
         for (int e = threadIdx.x; e < nt * pieces; e += blockDim.x) {
             const int tt = e / pieces, c = e % pieces;
-            cp_async_16(qs + tt * DKP + 4 * c, qr + g0 + (size_t)tt * H * dk + 4 * c);
-            cp_async_16(ks + tt * DKP + 4 * c, kr + g0 + (size_t)tt * H * dk + 4 * c);
+            cp_async_16(qs + tt * DKP + 4 * c, qr + g0 + (size_t)tt * Hq * dk + 4 * c);
+            cp_async_16(ks + tt * DKP + 4 * c, kr + g0 + (size_t)tt * Hq * dk + 4 * c);
         }
         cp_async_commit();
+        float* gs = vs + ST * C;
+        for (int e = threadIdx.x; e < nt; e += blockDim.x) {
+            const size_t at = (size_t)(t_first + t0 + e) * H + h;
+            gs[e] = tg.decay ? tg.decay[at] : dec_fixed;
+            gs[ST + e] = tg.kscale ? tg.kscale[at] : 1.f;
+        }
         for (int e = threadIdx.x; e < nt * C; e += blockDim.x) {
             const int tt = e / C, c = blockIdx.x * C + e % C;
             vs[e] = c < dv ? to_float(v[(size_t)(t_first + t0 + tt) * v_ld + (size_t)h * dv + c]) : 0.f;
@@ -300,9 +327,11 @@ retention_scan4_kernel(const float* __restrict__ qr, const float* __restrict__ k
         const float* qs = sm + stage * stage_floats;
         const float* ks = qs + ST * DKP;
         const float* vs = ks + ST * DKP;
+        const float* gs = vs + ST * C;
         for (int tt = 0; tt < nt; ++tt) {
             const float4 v4 = *(const float4*)(vs + tt * C + 4 * g);
-            const float vj[4] = {v4.x, v4.y, v4.z, v4.w};
+            const float dec = gs[tt], ksc = gs[ST + tt];
+            const float vj[4] = {v4.x * ksc, v4.y * ksc, v4.z * ksc, v4.w * ksc};
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int m4 = 0; m4 < KPT / 4; ++m4) {
@@ -536,7 +565,7 @@ TNX_EXPORT int tnx_retention_scan_columns(int dv) { return dv >= 16 ? 16 : 8; }
 template <typename T>
 static int retention_scan_launch(const float* qr, const float* kr, const T* v, int v_ld, const float* decay, float* state,
                                  const int* q_start, const int* q_len, const int* state_slots, float* out, int n_requests,
-                                 int H, int dk, int dv, int stage_tokens, cudaStream_t stream) {
+                                 int H, int dk, int dv, int stage_tokens, TokenGates tg, cudaStream_t stream) {
     const int C = tnx_retention_scan_columns(dv);
     const dim3 grid((dv + C - 1) / C, H, n_requests);
     const bool vec = dk % 4 == 0 && ((uintptr_t)qr % 16) == 0 && ((uintptr_t)kr % 16) == 0 && ((uintptr_t)state % 16) == 0;
@@ -544,37 +573,37 @@ static int retention_scan_launch(const float* qr, const float* kr, const T* v, i
                         ((size_t)dv * sizeof(T)) % 16 == 0;
 #define SCAN(KPT, R)                                                                                                    \
     do {                                                                                                                \
-        const size_t smem = ((size_t)SCAN_STAGES * stage_tokens * (2 * (KPT) * (R) + C) + (size_t)stage_tokens * C * (R)) * sizeof(float);                  \
+        const size_t smem = ((size_t)SCAN_STAGES * (stage_tokens * (2 * (KPT) * (R) + C) + token_gate_floats(stage_tokens)) + (size_t)stage_tokens * C * (R)) * sizeof(float); \
         if (vec && vasync) {                                                                                            \
             if (smem > 48 * 1024)                                                                                       \
                 cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, true, true>, grid, dim3(C * (R)), smem, stream, \
                                        qr, kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C,   \
-                                       stage_tokens);                                                                   \
+                                       stage_tokens, tg);                                                               \
         }                                                                                                               \
         if (vec) {                                                                                                      \
             if (smem > 48 * 1024)                                                                                       \
                 cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, true, false>, grid, dim3(C * (R)), smem, stream, \
                                        qr, kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C,   \
-                                       stage_tokens);                                                                   \
+                                       stage_tokens, tg);                                                               \
         }                                                                                                               \
         if (smem > 48 * 1024)                                                                                           \
             cudaFuncSetAttribute(retention_scan_kernel<T, KPT, R, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         return tnx_launch_in_order(retention_scan_kernel<T, KPT, R, false, false>, grid, dim3(C * (R)), smem, stream, qr, kr, \
-                                   v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C, stage_tokens); \
+                                   v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C, stage_tokens, tg); \
     } while (0)
 #define SCAN4(KPT, R, CC)                                                                                               \
     do {                                                                                                                \
         const int C4 = (CC);                                                                                            \
         const dim3 grid4((dv + C4 - 1) / C4, H, n_requests);                                                            \
-        const size_t smem = ((size_t)SCAN_STAGES * stage_tokens * (2 * (KPT) * (R) + C4) +                              \
+        const size_t smem = ((size_t)SCAN_STAGES * (stage_tokens * (2 * (KPT) * (R) + C4) + token_gate_floats(stage_tokens)) + \
                              (size_t)stage_tokens * (C4 / 4) * (4 * (R) + 4)) * sizeof(float);                          \
         if (smem > 48 * 1024)                                                                                           \
             cudaFuncSetAttribute(retention_scan4_kernel<T, KPT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         return tnx_launch_in_order(retention_scan4_kernel<T, KPT, R>, grid4, dim3((C4 / 4) * (R)), smem, stream, qr,    \
                                    kr, v, v_ld, decay, state, q_start, q_len, state_slots, out, H, dk, dv, C4,          \
-                                   stage_tokens);                                                                       \
+                                   stage_tokens, tg);                                                                   \
     } while (0)
     // Measured (32 heads of 128 x 128): a step of single tokens streams the state at 6.2 TB/s in the four-column form
     // (43 us for 64 requests); portions of prompts are a chain of dependent tokens in either form, and there the
@@ -599,17 +628,22 @@ static int retention_scan_launch(const float* qr, const float* kr, const T* v, i
 
 TNX_EXPORT int tnx_retention_scan(const float* qr, const float* kr, const void* v, int v_ld, const float* decay,
                                   float* state, const int* q_start, const int* q_len, const int* state_slots, float* out,
-                                  int n_requests, int H, int dk, int dv, int most_tokens, int v_h16, cudaStream_t stream) {
+                                  int n_requests, int H, int dk, int dv, int most_tokens, int v_h16,
+                                  const float* decay_tok, const float* kscale_tok, int qk_heads, cudaStream_t stream) {
     // most_tokens: an upper bound of the requests' rows (1 for a step of single tokens); it sizes the stages.
+    // decay_tok, kscale_tok [tokens, H]: a decay and a key scale per token (absent: decay[h], 1); qk_heads: how many
+    // heads q and k have (H, or fewer when groups of heads share them).
     if (n_requests <= 0) return 0;
     if (H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || n_requests > 65535 || most_tokens <= 0) return TNX_ERR_BAD_ARG;
+    if (qk_heads <= 0 || H % qk_heads || (!decay && !decay_tok)) return TNX_ERR_BAD_ARG;
+    const TokenGates tg{decay_tok, kscale_tok, qk_heads};
     int stage_tokens = 1;
     while (stage_tokens < most_tokens && stage_tokens < SCAN_TOKENS_MOST) stage_tokens *= 2;
     if (v_h16)
         return retention_scan_launch<h16>(qr, kr, (const h16*)v, v_ld, decay, state, q_start, q_len, state_slots, out,
-                                          n_requests, H, dk, dv, stage_tokens, stream);
+                                          n_requests, H, dk, dv, stage_tokens, tg, stream);
     return retention_scan_launch<float>(qr, kr, (const float*)v, v_ld, decay, state, q_start, q_len, state_slots, out,
-                                        n_requests, H, dk, dv, stage_tokens, stream);
+                                        n_requests, H, dk, dv, stage_tokens, tg, stream);
 }
 
 TNX_EXPORT int tnx_headwise_gated_rms_norm(const float* o, const void* gate, int gate_ld, const int* token_request,

@@ -1,6 +1,6 @@
 // RMS norm over the hidden axis, in 32-bit from the 32-bit residual stream, optionally of a sum:
 //   y = x_scale * x + delta          (delta: what a sublayer produced; absent: y = x_scale * x)
-//   out = y / sqrt(mean(y^2) + eps) * (w + w_offset)        (w absent: no scale)
+//   out = y / sqrt(mean(y^2) + eps) * (w + w_offset) * out_scale        (w absent: no weight)
 // One thread block per row; the row is kept in shared memory between the two passes, so out_f32
 // may be x itself (a post-norm block normalises its residual stream in place).
 // `rows`, when given, picks the input rows (the rows whose logits are wanted).
@@ -9,7 +9,7 @@
 template <typename TA, bool VEC>
 __global__ void rms_norm_kernel(const float* __restrict__ x, float x_scale, const float* __restrict__ delta,
                                 const int* __restrict__ rows, const float* __restrict__ w, float w_offset, float eps,
-                                float* out_f32, TA* __restrict__ out_act, int H) {
+                                float out_scale, float* out_f32, TA* __restrict__ out_act, int H) {
     extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -40,8 +40,49 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, float x_scale, cons
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float y = row[c] * rinv;
         if (w) y *= (w[c] + w_offset);
+        y *= out_scale;
         if (out_f32) out_f32[(size_t)r * H + c] = y;
         if (out_act) out_act[(size_t)r * H + c] = from_float<TA>(y);
+    }
+}
+
+// Two norms of the same row (the inputs of two sublayers that run side by side on one stream): the mean square is
+// formed once,  out1 = x / sqrt(ms + eps1) * (w1 + off1),  out2 = x / sqrt(ms + eps2) * (w2 + off2).
+template <typename TA>
+__global__ void rms_norm_pair_kernel(const float* __restrict__ x, const float* __restrict__ w1, float off1, float eps1,
+                                     const float* __restrict__ w2, float off2, float eps2, TA* __restrict__ out1,
+                                     TA* __restrict__ out2, int H) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t src = (size_t)blockIdx.x * H;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = x[src + c];
+        row[c] = v;
+        s += v * v;
+    }
+    const float ms = block_sum(s, scratch) / (float)H;
+    const float r1 = 1.0f / sqrtf(ms + eps1), r2 = 1.0f / sqrtf(ms + eps2);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = row[c];
+        out1[src + c] = from_float<TA>(v * r1 * (w1 ? w1[c] + off1 : 1.f));
+        if (out2) out2[src + c] = from_float<TA>(v * r2 * (w2 ? w2[c] + off2 : 1.f));
+    }
+}
+
+// x <- x + s1 * a (+ s2 * b): two sublayers' results, each multiplied channel by channel by a learned scale, enter
+// the 32-bit stream in one pass (s1, s2 absent: 1; b absent: one sublayer).
+__global__ void scaled_residual_add_kernel(float* x, const float* __restrict__ a, const float* __restrict__ s1,
+                                           const float* __restrict__ b, const float* __restrict__ s2, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t src = (size_t)blockIdx.x * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float d = a[src + c] * (s1 ? s1[c] : 1.f);
+        if (b) d = fmaf(b[src + c], s2 ? s2[c] : 1.f, d);
+        x[src + c] += d;
     }
 }
 
@@ -161,9 +202,35 @@ TNX_EXPORT int tnx_rms_norm_add(const float* x, float add_scale, const float* de
 #undef RMS_LAUNCH
 }
 
+TNX_EXPORT int tnx_rms_norm_pair(const float* x, const float* w1, float off1, float eps1, const float* w2, float off2,
+                                 float eps2, void* out1, void* out2, int n_rows, int H, int act_h16, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (H <= 0 || !x || !out1 || smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    if (act_h16) {
+        if (smem + 1024 > 48 * 1024)
+            cudaFuncSetAttribute(rms_norm_pair_kernel<h16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tnx_launch_ex(1, rms_norm_pair_kernel<h16>, dim3(n_rows), dim3(threads), smem, stream, x, w1, off1, eps1, w2,
+                             off2, eps2, (h16*)out1, (h16*)out2, H);
+    }
+    if (smem + 1024 > 48 * 1024)
+        cudaFuncSetAttribute(rms_norm_pair_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return tnx_launch_ex(1, rms_norm_pair_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, w1, off1, eps1, w2,
+                         off2, eps2, (float*)out1, (float*)out2, H);
+}
+
+TNX_EXPORT int tnx_scaled_residual_add(float* x, const float* a, const float* s1, const float* b, const float* s2,
+                                       int n_rows, int H, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || !x || !a) return TNX_ERR_BAD_ARG;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    return tnx_launch_ex(1, scaled_residual_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, a, s1, b, s2, H);
+}
+
 TNX_EXPORT int tnx_rms_norm(const float* x, float x_scale, const float* delta, const int* rows, const float* w,
-                            float w_offset, float eps, float* out_f32, void* out_act, int n_rows, int H, int act_h16,
-                            cudaStream_t stream) {
+                            float w_offset, float eps, float out_scale, float* out_f32, void* out_act, int n_rows, int H,
+                            int act_h16, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const size_t smem = (size_t)H * sizeof(float);
     if (H <= 0 || smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
@@ -174,7 +241,7 @@ TNX_EXPORT int tnx_rms_norm(const float* x, float x_scale, const float* delta, c
         if (smem + 1024 > 48 * 1024)                                                                                   \
             cudaFuncSetAttribute(rms_norm_kernel<TA, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
         return tnx_launch_ex(1, rms_norm_kernel<TA, V>, dim3(n_rows), dim3(threads), smem, stream, x, x_scale, delta,  \
-                             rows, w, w_offset, eps, out_f32, (TA*)out_act, H);                                        \
+                             rows, w, w_offset, eps, out_scale, out_f32, (TA*)out_act, H);                             \
     } while (0)
     if (act_h16) { if (vec) RMS_LAUNCH(h16, true); else RMS_LAUNCH(h16, false); }
     if (vec) RMS_LAUNCH(float, true); else RMS_LAUNCH(float, false);

@@ -53,6 +53,8 @@ SOURCES: Dict[str, str] = {
     "moe_grouped": "moe_grouped.cu",
     "latent_attention": "latent_attention.cu",
     "delta_rule": "delta_rule.cu",
+    "ssd": "ssd.cu",
+    "diff_attention": "diff_attention.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -121,8 +121,10 @@ def _rows_2d(t: torch.Tensor, name: str):
 
 
 # ---------------------------------------------------------------------------------------------
-def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_act, tok_scale=1.0):
-    """out[n] = tok_scale * (tok_table[ids[n]] or pre[n]) + pos_table[positions[n] + pos_offset]."""
+def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_act, tok_scale=1.0, sin_freq=None):
+    """out[n] = tok_scale * (tok_table[ids[n]] or pre[n]) + pos_table[positions[n] + pos_offset]; with sin_freq
+    (32-bit, one frequency per pair of columns) a sinusoidal vector is added as well: column 2i gets
+    sin(position * sin_freq[i]), column 2i + 1 the cosine."""
     lib = _lib("embedding", tok_table, pos_table, out_act)
     N = ids.shape[0]
     _need(ids, "ids", torch.int32, 1)
@@ -150,9 +152,12 @@ def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_ac
     if out_act is not None:
         _need(out_act, "out_act", _FLOATS, 2)
         act_bf16 = _is_h16(out_act)
+    if sin_freq is not None:
+        _f32_vec(sin_freq, "sin_freq", (H + 1) // 2)
+        _need(positions, "positions", torch.int32, 1)
     _check(lib.tnx_embed(_p(tok_table), _p(pre), _p(ids), _p(pos_table), _p(positions), c_int(pos_offset),
-                         c_float(float(tok_scale)), _p(out_f32), _p(out_act), c_int(N), c_int(H), c_int(table_bf16), c_int(act_bf16),
-                         _stream()), "embed")
+                         c_float(float(tok_scale)), _p(sin_freq), _p(out_f32), _p(out_act), c_int(N), c_int(H),
+                         c_int(table_bf16), c_int(act_bf16), _stream()), "embed")
 
 
 def patch_tokens(tokens, src, sampled):
@@ -791,10 +796,11 @@ def _f32_vec(t, name, n=None):
         raise KernelError(f"{name} has {t.shape[0]} elements, expected {n}")
 
 
-def rms_norm(x, weight, eps, out_f32=None, out_act=None, rows=None, x_scale=1.0, delta=None, weight_offset=0.0):
+def rms_norm(x, weight, eps, out_f32=None, out_act=None, rows=None, x_scale=1.0, delta=None, weight_offset=0.0,
+             out_scale=1.0):
     """Rows of y = x_scale * x + delta (delta optional, 32-bit like x) divided by their root mean square
-    (eps inside the root) and multiplied by (weight + weight_offset) when a weight is given.  out_f32 may
-    be x itself.  `rows` (int32) picks input rows."""
+    (eps inside the root) and multiplied by (weight + weight_offset) when a weight is given, then by out_scale.
+    out_f32 may be x itself.  `rows` (int32) picks input rows."""
     lib = _lib("rmsnorm", out_act)
     _need(x, "x", torch.float32, 2)
     H = x.shape[1]
@@ -812,8 +818,40 @@ def rms_norm(x, weight, eps, out_f32=None, out_act=None, rows=None, x_scale=1.0,
             if t.shape[0] < n_rows or t.shape[1] != H:
                 raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{n_rows}, {H}]")
     _check(lib.tnx_rms_norm(_p(x), c_float(x_scale), _p(delta), _p(rows), _p(weight), c_float(weight_offset),
-                            c_float(eps), _p(out_f32), _p(out_act), c_int(n_rows), c_int(H),
+                            c_float(eps), c_float(out_scale), _p(out_f32), _p(out_act), c_int(n_rows), c_int(H),
                             c_int(_is_h16(out_act) if out_act is not None else 0), _stream()), "rms_norm")
+
+
+def rms_norm_pair(x, weight1, offset1, eps1, out1, weight2=None, offset2=0.0, eps2=0.0, out2=None):
+    """Two RMS norms of the same rows of the 32-bit x with one pass over them (the inputs of two sublayers that read the
+    same stream): out_i = x / sqrt(mean(x^2) + eps_i) * (weight_i + offset_i), in the activation type.  out2 None: one."""
+    lib = _lib("rmsnorm", out1, out2)
+    _need(x, "x", torch.float32, 2)
+    N, H = x.shape
+    _f32_vec(weight1, "weight1", H); _f32_vec(weight2, "weight2", H)
+    for t, nm in ((out1, "out1"), (out2, "out2")):
+        if t is not None:
+            _need(t, nm, out1.dtype if nm == "out2" else _FLOATS, 2)
+            if tuple(t.shape) != (N, H):
+                raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{N}, {H}]")
+    _check(lib.tnx_rms_norm_pair(_p(x), _p(weight1), c_float(offset1), c_float(eps1), _p(weight2), c_float(offset2),
+                                 c_float(eps2), _p(out1), _p(out2), c_int(N), c_int(H), c_int(_is_h16(out1)), _stream()),
+           "rms_norm_pair")
+
+
+def scaled_residual_add(x, a, scale_a=None, b=None, scale_b=None):
+    """x += scale_a * a (+ scale_b * b), all 32-bit; the scales are vectors over the hidden axis (None: 1)."""
+    lib = _build.load("rmsnorm")
+    _need(x, "x", torch.float32, 2)
+    N, H = x.shape
+    for t, nm in ((a, "a"), (b, "b")):
+        if t is not None:
+            _need(t, nm, torch.float32, 2)
+            if tuple(t.shape) != (N, H):
+                raise KernelError(f"{nm} must have the shape of x")
+    _f32_vec(scale_a, "scale_a", H); _f32_vec(scale_b, "scale_b", H)
+    _check(lib.tnx_scaled_residual_add(_p(x), _p(a), _p(scale_a), _p(b), _p(scale_b), c_int(N), c_int(H), _stream()),
+           "scaled_residual_add")
 
 
 def rms_norm_add(x, add_scale, delta, weight, eps, out_f32=None, out_act=None, weight_offset=0.0, then=None):
@@ -886,9 +924,14 @@ def conv_qkv_prep(proj, col0, conv_w, taps, state, ctx, q_norm, k_norm, eps, inv
     add_launches(update)
 
 
-def moe_route(h, router, token_request, ids, weights, top, softmax_scores=False, renormalize=False):
+def moe_route(h, router, token_request, ids, weights, top, softmax_scores=False, renormalize=False, correction=None,
+              n_groups=1, keep_groups=1, group_top=2, renorm_eps=0.0, weight_scale=1.0):
     """For every row of h [N, W]: the `top` experts with the largest scores (sigmoid, or softmax, of the 32-bit product
-    with router [E, W]) into ids [N, top] (int32; -1 for a padded row) and their scores into weights [N, top]."""
+    with router [E, W]) into ids [N, top] (int32; -1 for a padded row) and their scores into weights [N, top].
+    correction (32-bit [E]): added to the sigmoid scores for the choice only.  n_groups > 1: the experts form equal groups
+    of neighbours, a group's score is the sum of its group_top largest choice scores, and only experts of the keep_groups
+    best groups can be chosen.  The weights are divided by (their sum + renorm_eps) with `renormalize`, then multiplied
+    by weight_scale."""
     lib = _lib("moe", h, router)
     _need(h, "h", _FLOATS, None, contiguous=False)
     N, W, ld = _rows_2d(h, "h")
@@ -900,24 +943,31 @@ def moe_route(h, router, token_request, ids, weights, top, softmax_scores=False,
     _need(ids, "ids", torch.int32, 2); _need(weights, "weights", torch.float32, 2)
     if tuple(ids.shape) != (N, top) or tuple(weights.shape) != (N, top):
         raise KernelError(f"ids and weights must be [{N}, {top}]")
+    _f32_vec(correction, "correction", E)
     _check(lib.tnx_moe_route(_p(h), c_int(ld), _p(router), _p(token_request), _p(ids), _p(weights), c_int(N), c_int(W),
                              c_int(E), c_int(top), c_int(1 if softmax_scores else 0), c_int(1 if renormalize else 0),
-                             c_int(_is_h16(h)), c_int(_is_h16(router)), _stream()), "moe_route")
+                             c_int(_is_h16(h)), c_int(_is_h16(router)), _p(correction), c_int(n_groups), c_int(keep_groups),
+                             c_int(group_top), c_float(renorm_eps), c_float(weight_scale), _stream()), "moe_route")
+
+
+EXPERT_FORMS = {"gated_swish": 0, "relu2": 1}
 
 
 def moe_experts(h, gate_up, down, ids, weights, y, out, gate_max, up_min, up_max, alpha, up_shift, weight_on_input=True,
-                accumulate=False, per_pair=None):
+                accumulate=False, per_pair=None, form="gated_swish"):
     """The chosen experts of every row, an expert's matrices streamed once for every four rows that chose it:
-    gate_up [E, 2F, W] (gate rows, then up rows), down [E, W, F]; y [N * top, F] scratch in h's type and per_pair
-    [N * top, W] 32-bit scratch (made here when not given); out 32-bit [N, W], written or added to."""
+    gate_up [E, 2F, W] (gate rows, then up rows; with form 'relu2', experts without a gate, [E, F, W]: the up rows
+    alone), down [E, W, F]; y [N * top, F] scratch in h's type and per_pair [N * top, W] 32-bit scratch (made here when
+    not given); out 32-bit [N, W], written or added to."""
     lib = _lib("moe", h, gate_up)
     _need(h, "h", _FLOATS, None, contiguous=False)
     N, W, ld = _rows_2d(h, "h")
     _need(gate_up, "gate_up", _FLOATS, 3); _need(down, "down", gate_up.dtype, 3)
     E, F2, Wg = gate_up.shape
-    F = F2 // 2
-    if Wg != W or F2 % 2 or tuple(down.shape) != (E, W, F):
-        raise KernelError(f"gate_up must be [E, 2F, {W}] and down [E, {W}, F]")
+    per = 1 if EXPERT_FORMS[form] else 2
+    F = F2 // per
+    if Wg != W or F2 % per or tuple(down.shape) != (E, W, F):
+        raise KernelError(f"gate_up must be [E, {per}F, {W}] and down [E, {W}, F]")
     top = ids.shape[1]
     _need(ids, "ids", torch.int32, 2); _need(weights, "weights", torch.float32, 2)
     _need(y, "y", h.dtype, 2); _need(out, "out", torch.float32, 2)
@@ -933,7 +983,8 @@ def moe_experts(h, gate_up, down, ids, weights, y, out, gate_max, up_min, up_max
                                c_int(N), c_int(W), c_int(F), c_int(top), c_int(E), c_float(gate_max), c_float(up_min),
                                c_float(up_max),
                                c_float(alpha), c_float(up_shift), c_int(1 if weight_on_input else 0),
-                               c_int(1 if accumulate else 0), c_int(_is_h16(h)), c_int(_is_h16(gate_up)), _stream()),
+                               c_int(1 if accumulate else 0), c_int(_is_h16(h)), c_int(_is_h16(gate_up)),
+                               c_int(EXPERT_FORMS[form]), _stream()),
            "moe_experts")
     add_launches(2)
 
@@ -944,7 +995,7 @@ def moe_grouped_supported(h, gate_up, down) -> bool:
     if h.dtype not in _H16 or gate_up.dtype != h.dtype or down.dtype != h.dtype:
         return False
     E, F2, W = gate_up.shape
-    return (W % 8 == 0 and (F2 // 2) % 8 == 0 and E <= 1024 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+    return (W % 8 == 0 and down.shape[2] % 8 == 0 and E <= 1024 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
             and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0 and E * max(F2, W) < 2 ** 31)
 
 
@@ -1002,7 +1053,7 @@ def gemm_tc_batched(x, x_head, w, out, out_head):
 
 
 def moe_grouped(ctx, h, gate_up, down, ids, weights, out, gate_max, up_min, up_max, alpha, up_shift, weight_on_input=True,
-                accumulate=False):
+                accumulate=False, form="gated_swish"):
     """moe_experts for many rows: the (row, expert) pairs sorted by expert into 128-row tiles, the experts' two
     products as grouped tensor-core products, the activation between them and the sum over a row's experts as
     kernels of csrc/moe_grouped.cu.  Buffers come from ctx.scratch; nothing is read on the host."""
@@ -1011,7 +1062,7 @@ def moe_grouped(ctx, h, gate_up, down, ids, weights, out, gate_max, up_min, up_m
         raise KernelError("the grouped form takes a 16-bit engine, experts stored in its type and widths that are multiples of 8")
     N, W = h.shape
     E, F2, _ = gate_up.shape
-    F, top = F2 // 2, ids.shape[1]
+    F, top = down.shape[2], ids.shape[1]
     P = N * top
     # the tile: the smallest that holds twice an expert's even share of the pairs (so that most experts take one tile and
     # their matrices are streamed once), 128 rows where the experts get many
@@ -1026,7 +1077,7 @@ def moe_grouped(ctx, h, gate_up, down, ids, weights, out, gate_max, up_min, up_m
     gu = ctx.scratch(rows, F2, h.dtype)
     gemm_tc_grouped(x, gate_up, gu, group_of_tile, tile, used)
     y = ctx.scratch(rows, F, h.dtype)
-    moe_activation(lib, gu, y, group_of_tile, tile, gate_max, up_min, up_max, alpha, up_shift)
+    moe_activation(lib, gu, y, group_of_tile, tile, gate_max, up_min, up_max, alpha, up_shift, form)
     per_pair = ctx.scratch(rows, W, torch.float32)
     gemm_tc_grouped(y, down, per_pair, group_of_tile, tile, used)
     moe_combine(lib, per_pair, row_of_pair, weights, out, accumulate, weight_on_input)
@@ -1041,9 +1092,10 @@ def moe_sort_rows(lib, h, ids, weights, n_experts, tiles, tile, group_of_tile, r
                               c_int(top), c_int(1 if weight_on_input else 0), _stream()), "moe_gather")
 
 
-def moe_activation(lib, gu, y, group_of_tile, tile, gate_max, up_min, up_max, alpha, up_shift):
+def moe_activation(lib, gu, y, group_of_tile, tile, gate_max, up_min, up_max, alpha, up_shift, form="gated_swish"):
     _check(lib.tnx_moe_act(_p(gu), _p(y), _p(group_of_tile), c_int(tile), c_int(gu.shape[0]), c_int(y.shape[1]), c_float(gate_max),
-                           c_float(up_min), c_float(up_max), c_float(alpha), c_float(up_shift), _stream()), "moe_act")
+                           c_float(up_min), c_float(up_max), c_float(alpha), c_float(up_shift), c_int(EXPERT_FORMS[form]),
+                           _stream()), "moe_act")
 
 
 def moe_combine(lib, per_pair, row_of_pair, weights, out, accumulate, weight_on_input):
@@ -1116,18 +1168,31 @@ def retention_prep(proj, q_off, k_off, token_request, positions, inv_freq, rot_d
                                   c_int(n_heads), c_int(k_dim), c_int(_is_h16(proj)), _stream()), "retention_prep")
 
 
-def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_heads, k_dim, v_dim, most_tokens=None):
+def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_heads, k_dim, v_dim, most_tokens=None,
+                   decay_tok=None, kscale_tok=None, qk_heads=None):
     """S <- decay S + k v^T, o = S^T q, token by token for every request of the step (q_start, q_len: its rows;
     q_len 0 or slot < 0: skipped).  q, k: 32-bit [N, n_heads * k_dim]; v: [N, n_heads * v_dim] view in the
     activation type or 32-bit; state: 32-bit [slots, n_heads, v_dim, k_dim]; out: 32-bit [N, n_heads * v_dim].
     most_tokens: an upper bound of any request's rows (default: N); a step of single tokens says 1 and gets
-    small stages."""
+    small stages.  decay_tok, kscale_tok (32-bit [N, n_heads]): S <- decay_tok S + kscale_tok k v^T with numbers of the
+    token (absent: decay[h], 1); qk_heads: q and k are [N, qk_heads * k_dim] and head h reads those of
+    h // (n_heads // qk_heads)."""
     lib = _lib("retention", v)
     N = q.shape[0]
+    qk_heads = n_heads if qk_heads is None else int(qk_heads)
+    if qk_heads <= 0 or n_heads % qk_heads:
+        raise KernelError(f"{n_heads} heads cannot share {qk_heads} heads of queries and keys")
+    for t, nm in ((decay_tok, "decay_tok"), (kscale_tok, "kscale_tok")):
+        if t is not None:
+            _need(t, nm, torch.float32, 2)
+            if tuple(t.shape) != (N, n_heads):
+                raise KernelError(f"{nm} must be [{N}, {n_heads}]")
+    if decay is None and decay_tok is None:
+        raise KernelError("a decay per head or per token is needed")
     for t, nm in ((q, "q"), (k, "k")):
         _need(t, nm, torch.float32, 2)
-        if tuple(t.shape) != (N, n_heads * k_dim):
-            raise KernelError(f"{nm} must be [{N}, {n_heads * k_dim}]")
+        if tuple(t.shape) != (N, qk_heads * k_dim):
+            raise KernelError(f"{nm} must be [{N}, {qk_heads * k_dim}]")
     _need(v, "v", _FLOATS, None, contiguous=False)
     Nv, wv, v_ld = _rows_2d(v, "v")
     if (Nv, wv) != (N, n_heads * v_dim):
@@ -1147,7 +1212,7 @@ def retention_scan(q, k, v, decay, state, q_start, q_len, state_slots, out, n_he
     _check(lib.tnx_retention_scan(_p(q), _p(k), _p(v), c_int(v_ld), _p(decay), _p(state), _p(q_start), _p(q_len),
                                   _p(state_slots), _p(out), c_int(R), c_int(n_heads), c_int(k_dim), c_int(v_dim),
                                   c_int(max(1, int(most_tokens if most_tokens is not None else N))), c_int(_is_h16(v)),
-                                  _stream()), "retention_scan")
+                                  _p(decay_tok), _p(kscale_tok), c_int(qk_heads), _stream()), "retention_scan")
 
 
 def retention_decode(proj, q_off, k_off, v_off, g_off, positions, inv_freq, rot_dims, k_scale, decay, state, q_start, q_len,
@@ -1208,6 +1273,118 @@ def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out,
                                            c_float(out_scale), _p(out), c_int(out_ld), c_int(N), c_int(n_heads),
                                            c_int(v_dim), c_int(activation_code(gate_activation)), c_int(_is_h16(out)),
                                            _stream()), "headwise_gated_rms_norm")
+
+
+def ssd_prep(proj, col0, conv_w, conv_b, taps, state, ctx, a_log, dt_bias, activation, x_out, b_out, c_out, dt_out,
+             decay_out, n_heads, v_dim, groups, state_dim):
+    """From the input projection's output `proj` [N, *] (from column col0 on: z | x | B | C | dt): x, B and C through
+    their short causal convolution (conv_w [taps, channels], conv_b [channels] or None, both 32-bit; state
+    [slots, taps - 1, channels] in proj's type) and the activation, as 32-bit x [N, heads * v_dim], B and C
+    [N, groups * state_dim]; dt = softplus(dt + dt_bias) and decay = exp(-exp(a_log) dt), 32-bit [N, heads]."""
+    lib = _lib("ssd", proj)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    H, P, G, Ns = n_heads, v_dim, groups, state_dim
+    inner, C = H * P, H * P + 2 * G * Ns
+    if col0 < 0 or col0 + inner + C + H > width:
+        raise KernelError("the projection is narrower than its columns")
+    _need(conv_w, "conv_w", torch.float32, 2)
+    if tuple(conv_w.shape) != (taps, C):
+        raise KernelError(f"conv_w must be [{taps}, {C}]")
+    _f32_vec(conv_b, "conv_b", C); _f32_vec(a_log, "a_log", H); _f32_vec(dt_bias, "dt_bias", H)
+    if taps > 1:
+        _need(state, "state", proj.dtype, 3)
+        if tuple(state.shape[1:]) != (taps - 1, C):
+            raise KernelError(f"state must be [slots, {taps - 1}, {C}]")
+    for t, nm, w in ((x_out, "x_out", inner), (b_out, "b_out", G * Ns), (c_out, "c_out", G * Ns), (dt_out, "dt_out", H),
+                     (decay_out, "decay_out", H)):
+        _need(t, nm, torch.float32, 2)
+        if tuple(t.shape) != (N, w):
+            raise KernelError(f"{nm} must be [{N}, {w}]")
+    for t, nm in ((ctx.token_request, "token_request"), (ctx.positions, "positions"), (ctx.q_start, "q_start"),
+                  (ctx.q_len, "q_len"), (ctx.state_slots, "state_slots")):
+        _need(t, nm, torch.int32, 1)
+    _check(lib.tnx_ssd_prep(_p(proj), c_int(ld), c_int(col0), _p(conv_w), _p(conv_b), c_int(taps),
+                            _p(state if taps > 1 else None), _p(ctx.token_request), _p(ctx.positions), _p(ctx.q_start),
+                            _p(ctx.q_len), _p(ctx.state_slots), _p(a_log), _p(dt_bias), c_int(activation_code(activation)),
+                            _p(x_out), _p(b_out), _p(c_out), _p(dt_out), _p(decay_out), c_int(N), c_int(H), c_int(P),
+                            c_int(G), c_int(Ns), c_int(_is_h16(proj)), _stream()), "ssd_prep")
+    if taps > 1 and not ctx.decode_only:
+        conv_state_update(proj, col0 + inner, state, ctx)
+
+
+def ssd_gate_norm(y, x, skip, z, token_request, weight, eps, activation, out, v_dim, parts):
+    """out = rms_in_parts((y + skip[head] * x) * act(z)) * weight: y and x 32-bit [N, inner], z and out views in the
+    activation type, the root mean square taken over each of `parts` equal parts of the inner width."""
+    lib = _lib("ssd", z, out)
+    _need(y, "y", torch.float32, 2)
+    N, inner = y.shape
+    if skip is not None:
+        _need(x, "x", torch.float32, 2)
+        if tuple(x.shape) != (N, inner) or inner % v_dim:
+            raise KernelError(f"x must be [{N}, {inner}]")
+        _f32_vec(skip, "skip", inner // v_dim)
+    _need(z, "z", out.dtype, None, contiguous=False)
+    Nz, wz, z_ld = _rows_2d(z, "z")
+    _need(out, "out", _FLOATS, None, contiguous=False)
+    No, wo, out_ld = _rows_2d(out, "out")
+    if (Nz, wz) != (N, inner) or (No, wo) != (N, inner):
+        raise KernelError(f"z and out must be [{N}, {inner}]")
+    _f32_vec(weight, "weight", inner)
+    _check(lib.tnx_ssd_gate_norm(_p(y), _p(x), _p(skip), _p(z), c_int(z_ld), _p(token_request), _p(weight), c_float(eps),
+                                 c_int(activation_code(activation)), _p(out), c_int(out_ld), c_int(N), c_int(inner),
+                                 c_int(v_dim), c_int(parts), c_int(_is_h16(out)), _stream()), "ssd_gate_norm")
+
+
+def diff_qkv_prep(proj, col0, token_request, positions, q_norm, k_norm, eps, temp_coef, temp_every, q_out, k_out, v_out,
+                  n_heads, n_kv_heads, k_dim, v_dim, pad_dim):
+    """Queries, keys and values of differential attention from one product's output `proj` [N, *] (from column col0 on:
+    queries [heads][2][k_dim], then, unless n_kv_heads is 0, keys [kv_heads][2][k_dim] and values [kv_heads][v_dim]):
+    per head and map an RMS norm with one weight vector (q_norm, k_norm [k_dim]; None: no weight), queries times
+    1 + temp_coef ln(floor((p + 1) / temp_every) + 1) (temp_every 0: not), written for ONE paged attention call with
+    2 heads query heads of pad_dim dims: q_out [N, 2 heads * pad_dim] (map m of a head in columns m k_dim ..), k_out
+    [N, kv_heads * pad_dim] (both maps side by side), v_out the same shape."""
+    lib = _lib("diff_attention", proj, q_out)
+    _need(proj, "proj", _FLOATS, None, contiguous=False)
+    N, width, ld = _rows_2d(proj, "proj")
+    H, G, dk, dv, D = n_heads, n_kv_heads, k_dim, v_dim, pad_dim
+    if col0 < 0 or col0 + 2 * H * dk + G * (2 * dk + dv) > width:
+        raise KernelError("the projection is narrower than its q/k/v columns")
+    outs = [(q_out, "q_out", 2 * H * D)] + ([(k_out, "k_out", G * D), (v_out, "v_out", G * D)] if G else [])
+    for t, nm, w in outs:
+        _need(t, nm, proj.dtype, 2)
+        if tuple(t.shape) != (N, w):
+            raise KernelError(f"{nm} must be [{N}, {w}]")
+    _f32_vec(q_norm, "q_norm", dk); _f32_vec(k_norm, "k_norm", dk)
+    _need(token_request, "token_request", torch.int32, 1); _need(positions, "positions", torch.int32, 1)
+    _check(lib.tnx_diff_qkv_prep(_p(proj), c_int(ld), c_int(col0), _p(token_request), _p(positions), _p(q_norm), _p(k_norm),
+                                 c_float(eps), c_float(temp_coef), c_int(temp_every), _p(q_out), _p(k_out if G else None),
+                                 _p(v_out if G else None), c_int(N), c_int(H), c_int(G), c_int(dk), c_int(dv), c_int(D),
+                                 c_int(_is_h16(proj)), _stream()), "diff_qkv_prep")
+
+
+def diff_combine(att, gate, token_request, lam, eps, out_mult, out_scale, out, n_heads, v_dim, pad_dim):
+    """From the attention's output att [N, 2 heads * pad_dim] (query head 2 h + map): o = a1 - lam a2 over the first v_dim
+    dims, divided by its root mean square, times out_mult, times sigmoid(gate[n, h]) (gate [N, heads] view or None),
+    times out_scale, into out [N, heads * v_dim] (a view with contiguous rows)."""
+    lib = _lib("diff_attention", att, out)
+    _need(att, "att", _FLOATS, 2)
+    N = att.shape[0]
+    if att.shape[1] != 2 * n_heads * pad_dim:
+        raise KernelError(f"att must be [{N}, {2 * n_heads * pad_dim}]")
+    gate_ld = 0
+    if gate is not None:
+        _need(gate, "gate", att.dtype, None, contiguous=False)
+        Ng, wg, gate_ld = _rows_2d(gate, "gate")
+        if (Ng, wg) != (N, n_heads):
+            raise KernelError(f"gate must be [{N}, {n_heads}]")
+    _need(out, "out", att.dtype, None, contiguous=False)
+    No, wo, out_ld = _rows_2d(out, "out")
+    if (No, wo) != (N, n_heads * v_dim):
+        raise KernelError(f"out must be [{N}, {n_heads * v_dim}]")
+    _check(lib.tnx_diff_combine(_p(att), _p(gate), c_int(gate_ld), _p(token_request), c_float(lam), c_float(eps),
+                                c_float(out_mult), c_float(out_scale), _p(out), c_int(out_ld), c_int(N), c_int(n_heads),
+                                c_int(v_dim), c_int(pad_dim), c_int(_is_h16(att)), _stream()), "diff_combine")
 
 
 def mingru_scan(proj, z_off, x_off, g_off, state, q_start, q_len, state_slots, out, width, out_scale=1.0,

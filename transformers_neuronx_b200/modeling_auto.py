@@ -1,7 +1,7 @@
 """The entry-point class of a model folder, chosen by its config.json.
 
 The reference maps `model_type` to one of its sampling classes
-(src/transformers_neuronx/modeling_auto.py:5-47).  Here the table holds OPT, Vononex, Pifelix and Tutelix; another architecture
+(src/transformers_neuronx/modeling_auto.py:5-47).  Here the table holds OPT, Vononex, Pifelix, Tutelix and Vozirax; another architecture
 registers its own entry-point class beside its registration in config/registry.py.
 """
 from __future__ import annotations
@@ -24,6 +24,7 @@ def _ensure_builtin() -> None:
     from .vononex import model as _vononex  # noqa: F401  registers VononexForSampling
     from .pifelix import model as _pifelix  # noqa: F401  registers PifelixForSampling
     from .tutelix import model as _tutelix  # noqa: F401  registers TutelixForSampling
+    from .vozirax import model as _vozirax  # noqa: F401  registers VoziraxForSampling
 
 
 class NeuronAutoModelForCausalLM:

@@ -7,4 +7,5 @@ from . import norm, position, attention, feedforward, block, embedding   # regis
 from . import rotary_attention, retention, mingru, parallel, conv_attention   # noqa: F401  more built-in mixers
 from . import moe   # noqa: F401  the feed-forward of routed experts
 from . import latent_attention, delta_rule   # noqa: F401  attention through latents; the gated delta rule
+from . import ssd, diff_attention   # noqa: F401  the selective state-space mixer; differential attention
 from .embedding import Embedding, Head

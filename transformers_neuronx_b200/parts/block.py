@@ -19,13 +19,22 @@ sandwich_norm:                                            x = x + norm1_post(mix
     goes into a 32-bit buffer; one kernel normalises it, adds it to the stream and, where the next sublayer of the
     same layer follows, applies that sublayer's input norm to the new row (Norm.forward_add(..., then=norm2)).
 
+parallel_residual:                                        x = x + s1 * mixer(norm1(x)) + s2 * ff(norm2(x))
+    both sublayers read the same x, each behind a norm of its own (one kernel forms both norms: the mean square of a row
+    is the same for both), and their results, multiplied channel by channel by learned vectors s1 and s2 (the layer's
+    spec names the tensors; absent: 1), enter the stream in one pass.  A layer may have no feed-forward.
+
 `x` is the 32-bit residual stream and is updated in place; `x_act` is its copy in the activation
 type, which a block that feeds x itself into a matrix product needs on entry
 (``needs_act_input``) and keeps current (``keeps_act_current``).
 """
 from __future__ import annotations
 
-from .base import NormedInput
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorSpec
+from .base import NormedInput, Part, to_device
 from .registry import register_block
 
 
@@ -165,7 +174,64 @@ class SandwichNormBlock(ScaledPostNormBlock):
         self.norm2_post.forward_add(ctx, x, 1.0, out, out_f32=x)
 
 
+class ChannelScale(Part):
+    """A learned vector over the hidden axis that multiplies a sublayer's result (kept in 32-bit)."""
+    graph_safe = True
+
+    def __init__(self, name: str, size: int):
+        self.name, self.size = name, size
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.size,), "norm_weight")]
+
+    def load(self, tensors, device, act_dtype):
+        self.weight = to_device(tensors[self.name], device, torch.float32)
+
+    def parameter_bytes(self):
+        return self.weight.numel() * 4 if self.weight is not None else 0
+
+
+class ParallelResidualBlock(ScaledPostNormBlock):
+    """x <- x + s1 * mixer(norm1(x)) + s2 * ff(norm2(x)), both sublayers on the same x."""
+    needs_act_input = False
+    keeps_act_current = False
+    takes_layer_spec = True
+
+    def __init__(self, norm1, mixer, norm2, feed_forward, layer_spec=None):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        need = [norm1] + ([norm2] if feed_forward is not None else [])
+        for n in need:
+            if n is None or not hasattr(n, "forward_pair"):
+                raise ValueError("a parallel_residual block needs a norm before each sublayer that can share a kernel with "
+                                 f"the other; {type(n).__name__} does not")
+        size = norm1.spec.size
+        s1, s2 = getattr(layer_spec, "scale1", None), getattr(layer_spec, "scale2", None)
+        self.scale1 = ChannelScale(s1, size) if s1 else None
+        self.scale2 = ChannelScale(s2, size) if (s2 and feed_forward is not None) else None
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.scale1, self.norm2, self.feed_forward, self.scale2)
+                if p is not None]
+
+    def forward(self, ctx, x, x_act):
+        N, W = x.shape
+        h1 = ctx.scratch(N, W)
+        two = self.feed_forward is not None
+        h2 = ctx.scratch(N, W) if two else None
+        self.norm1.forward_pair(ctx, x, h1, self.norm2 if two else None, h2)
+        a = ctx.scratch(N, W, x.dtype)
+        self._run(ctx, self.mixer, h1, a)
+        b = None
+        if two:
+            b = ctx.scratch(N, W, x.dtype)
+            self._run(ctx, self.feed_forward, h2, b)
+        ops.scaled_residual_add(x, a, self.scale1.weight if self.scale1 else None, b,
+                                self.scale2.weight if self.scale2 else None)
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("parallel_residual", ParallelResidualBlock)
 register_block("sandwich_norm", SandwichNormBlock)
 register_block("output_norm", OutputNormBlock)
 register_block("post_norm_scaled", ScaledPostNormBlock)

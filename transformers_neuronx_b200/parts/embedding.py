@@ -69,8 +69,10 @@ class Embedding(Part):
             pre = ctx.empty(ctx.n_tokens, x.shape[1], torch.float32)
             self.project_in.forward(e, pre)
             tok = None
-        ops.embed(tok, pre, ctx.token_ids, pos_table, ctx.positions, offset, x, x_act, tok_scale=self.spec.scale)
-        if self.position is not None and table_pos is None:
+        freq = getattr(self.position, "frequencies_for_embedding", lambda: None)() if self.position is not None else None
+        ops.embed(tok, pre, ctx.token_ids, pos_table, ctx.positions, offset, x, x_act, tok_scale=self.spec.scale,
+                  sin_freq=freq)
+        if self.position is not None and table_pos is None and freq is None:
             self.position.embed(ctx, x)
             if x_act is not None:
                 ops.pick_rows(x, None, out_act=x_act)
@@ -83,6 +85,8 @@ class Head(Part):
         self.weight = None
         self.final_norm = build_part("norm", spec.final_norm) if spec.final_norm else None
         self.project_out = Linear(spec.project_out) if spec.project_out else None
+        if float(spec.logit_scale) != 1.0 and (self.final_norm is None or not getattr(self.final_norm, "takes_out_scale", False)):
+            raise ValueError("a head that multiplies its logits by a constant needs a final norm whose kernel applies it")
 
     @property
     def libraries(self):
@@ -122,7 +126,11 @@ class Head(Part):
         """32-bit logits [len(rows), vocab] of the picked rows of the residual stream."""
         R = rows.shape[0]
         y = ctx.empty(R, x.shape[1])
-        if self.final_norm is not None:
+        scale = float(self.spec.logit_scale)
+        if self.final_norm is not None and scale != 1.0:
+            # the constant rides on the norm's 32-bit output: the product that follows is linear
+            self.final_norm.forward(ctx, x, out_act=y, rows=rows, out_scale=scale)
+        elif self.final_norm is not None:
             self.final_norm.forward(ctx, x, out_act=y, rows=rows)
         else:
             ops.pick_rows(x, rows, out_act=y)

@@ -51,6 +51,7 @@ class LayerNorm(Norm):
 
 class RMSNorm(Norm):
     graph_safe = True
+    takes_out_scale = True            # forward(..., out_scale=c) multiplies the result by a constant in the same kernel
     libraries = ("rmsnorm",)
 
     def __init__(self, spec: NormSpec):
@@ -70,9 +71,18 @@ class RMSNorm(Norm):
     def parameter_bytes(self):
         return self.weight.numel() * 4 if self.weight is not None else 0
 
-    def forward(self, ctx, x, out_f32=None, out_act=None, rows=None):
+    def forward(self, ctx, x, out_f32=None, out_act=None, rows=None, out_scale=1.0):
         ops.rms_norm(x, self.weight, self.spec.eps, out_f32=out_f32, out_act=out_act, rows=rows,
-                     weight_offset=self.spec.weight_offset)
+                     weight_offset=self.spec.weight_offset, out_scale=out_scale)
+
+    def forward_pair(self, ctx, x, out1, other=None, out2=None):
+        """This norm and `other` (an RMSNorm) of the same rows in one kernel: the inputs of two sublayers side by side."""
+        if other is not None and not isinstance(other, RMSNorm):
+            raise ValueError(f"only RMS norms share a kernel, not {type(other).__name__}")
+        o = other.spec if other is not None else None
+        ops.rms_norm_pair(x, self.weight, self.spec.weight_offset, self.spec.eps, out1,
+                          other.weight if other is not None else None, o.weight_offset if o else 0.0,
+                          o.eps if o else 0.0, out2 if other is not None else None)
 
     def forward_sum(self, ctx, x, x_scale, delta, out_f32=None, out_act=None):
         """norm(x_scale * x + delta) in one kernel; out_f32 may be x."""

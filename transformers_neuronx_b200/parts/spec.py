@@ -54,12 +54,13 @@ class RotarySpec:
 
 @dataclass(frozen=True)
 class PositionSpec:
-    kind: str                        # 'learned' | 'none' | a registered kind
+    kind: str                        # 'learned' | 'sinusoidal' | 'none' | a registered kind
     table: Optional[str] = None      # tensor name, [rows, dim]
     rows: int = 0
     dim: int = 0
     offset: int = 0                  # row = position + offset
     extra: Tuple = ()
+    base: float = 10000.0            # 'sinusoidal': entry 2i = sin(p base^(-2i/dim)), entry 2i + 1 = cos of the same
 
 
 @dataclass(frozen=True)
@@ -206,6 +207,72 @@ class ConvAttentionSpec:
 
 
 @dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Differential softmax attention over the paged cache: every head holds TWO maps of queries and keys (k_dim dims
+    each, the projections' rows laid out head by head as [map 1, map 2]) over the same values,
+        o = softmax(scale q1 k1^T) v - lambda softmax(scale q2 k2^T) v,   lambda = exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff,
+    then each head's o is divided by its root mean square (no weight), multiplied by out_mult and by the sigmoid of the
+    head's entry of a gate projection, before the output projection.  Queries and keys are normalised per head and map
+    (one weight vector of k_dim for all), and queries are multiplied by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1)
+    at position p (temp_every 0: not).  Positions enter in no other way.  With `kv_source` the mixer has no keys and
+    values of its own: it reads the pages of the mixer whose schedule entry has that cache number."""
+    kind: str                        # 'diff_attention'
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    k_dim: int                       # per map
+    v_dim: int
+    scale: float
+    diff: float                      # the constant of lambda
+    out_mult: float                  # what the normalised head output is multiplied by
+    q: LinearSpec = None             # [n_heads * 2 * k_dim, hidden]
+    k: Optional[LinearSpec] = None   # [n_kv_heads * 2 * k_dim, hidden]
+    v: Optional[LinearSpec] = None   # [n_kv_heads * v_dim, hidden]
+    gate: Optional[LinearSpec] = None   # [n_heads, hidden]; None: no output gate
+    out: LinearSpec = None
+    q_norm: Optional[str] = None     # tensor [k_dim]
+    k_norm: Optional[str] = None
+    lambda_q1: str = None            # tensors [k_dim]
+    lambda_k1: str = None
+    lambda_q2: str = None
+    lambda_k2: str = None
+    norm_eps: float = 1e-6
+    temp_coef: float = 0.0
+    temp_every: int = 0
+    window: Optional[int] = None
+    kv_source: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class SSDSpec:
+    """A selective state-space recurrence with one decay per head and token ("state-space duality").  The input
+    projection's rows are [z: inner | x: inner | B: groups * state | C: groups * state | dt: n_heads], inner = n_heads * v_dim.
+    x, B and C pass one short causal convolution per channel (with bias) and an activation; dt <- softplus(dt + dt_bias);
+    per head h (group h / (n_heads / groups)), with S of state x v_dim:
+        S <- exp(-exp(A_log_h) dt) S + dt B x^T;   y = S^T C + D_h x
+    y times act(z) (the gate comes first), then divided by its root mean square in `norm_groups` equal parts of the
+    inner width, times a weight vector, then the output projection."""
+    kind: str                        # 'ssd'
+    hidden: int
+    n_heads: int
+    v_dim: int
+    state: int
+    groups: int
+    norm_groups: int
+    conv_taps: int
+    in_proj: LinearSpec = None       # [2 inner + 2 groups state + n_heads, hidden]
+    out: LinearSpec = None
+    conv: str = None                 # tensor [inner + 2 groups state, conv_taps]; the last column weighs the current token
+    conv_bias: Optional[str] = None  # tensor [inner + 2 groups state]
+    dt_bias: str = None              # tensor [n_heads]
+    a_log: str = None                # tensor [n_heads]
+    skip: Optional[str] = None       # tensor [n_heads]: D
+    out_norm: Optional[str] = None   # tensor [inner]
+    norm_eps: float = 1e-6
+    activation: str = "silu"         # of the convolution's output and of the gate
+
+
+@dataclass(frozen=True)
 class RetentionSpec:
     """Linear attention with a fixed decay per head: S <- decay S + k v^T, o = S^T q; each head's o divided by
     its root mean square, gated by silu of a projection, then the output projection."""
@@ -256,8 +323,8 @@ class GatedFeedForwardSpec:
 
 @dataclass(frozen=True)
 class ExpertSpec:
-    gate: str                        # tensor names, [ff, hidden], [ff, hidden], [hidden, ff]; no biases
-    up: str
+    gate: Optional[str]              # tensor names, [ff, hidden], [ff, hidden], [hidden, ff]; no biases
+    up: str                          # (gate None: an expert without a gate, see RoutedFeedForwardSpec.expert_form)
     down: str
 
 
@@ -266,7 +333,13 @@ class RoutedFeedForwardSpec:
     """Experts chosen per token by a router: scores = sigmoid (or softmax) of router(h) in 32-bit, the `top` largest
     choose, their scores are the weights (divided by their sum with `renormalize`).  An expert computes
     down(g * sigmoid(act_alpha g) * (u + up_shift)) with g = min(gate(x), gate_limit) and u = clamp(up(x), +-up_limit);
-    the weight multiplies the expert's input x = w h (`weight_on_input`) or its output."""
+    the weight multiplies the expert's input x = w h (`weight_on_input`) or its output.
+    With `expert_form` 'relu2' an expert has no gate: down(relu(up(x))^2).
+    Routing options (sigmoid scores): `correction` names a tensor [n_experts] that is added to the scores for the CHOICE
+    only (the weights stay the uncorrected scores); with `n_groups` > 1 the experts form equal groups of neighbours, a
+    group's score is the sum of its `group_top` largest choice scores, and only experts of the `keep_groups` best groups
+    can be chosen; the weights are divided by (their sum + renorm_eps) with `renormalize`, then multiplied by
+    `weight_scale`."""
     kind: str                        # 'routed_experts'
     hidden: int
     ff: int
@@ -281,6 +354,13 @@ class RoutedFeedForwardSpec:
     up_limit: Optional[float] = None
     act_alpha: float = 1.702
     up_shift: float = 1.0
+    expert_form: str = "gated_swish"  # 'gated_swish' | 'relu2'
+    correction: Optional[str] = None
+    n_groups: int = 1
+    keep_groups: int = 1
+    group_top: int = 2
+    renorm_eps: float = 0.0
+    weight_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -293,7 +373,7 @@ class DenseFeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    block: str                       # 'pre_norm' | 'post_norm' | 'post_norm_scaled' | 'output_norm' | 'sandwich_norm' | a registered kind
+    block: str                       # 'pre_norm' | 'post_norm' | 'post_norm_scaled' | 'output_norm' | 'sandwich_norm' | 'parallel_residual' | a registered kind
     norm1: Any = None
     mixer: Any = None
     norm2: Any = None
@@ -302,6 +382,8 @@ class LayerSpec:
     norm2_post: Any = None           #     x <- x + norm1_post(mixer(norm1(x))); x <- x + norm2_post(ff(norm2(x)))
     residual_scale: float = 1.0      # 'post_norm_scaled': x <- norm(residual_scale * x + sublayer(x));
                                      # 'output_norm': x <- x + residual_scale * norm(sublayer(x))
+    scale1: Optional[str] = None     # 'parallel_residual': tensors [hidden] that multiply the mixer's and the
+    scale2: Optional[str] = None     #     feed-forward's result, x <- x + scale1 * mixer(norm1(x)) + scale2 * ff(norm2(x))
 
 
 @dataclass(frozen=True)
@@ -322,6 +404,7 @@ class HeadSpec:
     tied_to: Optional[str] = None    # used when the file does not store `weight`
     final_norm: Optional[NormSpec] = None
     project_out: Optional[LinearSpec] = None
+    logit_scale: float = 1.0         # the logits are multiplied by it
 
 
 @dataclass(frozen=True)
