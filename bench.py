@@ -21,6 +21,8 @@ Pifelix decoder (attention behind convolved projections under a chunked mask, tw
 layer's pages, eight experts of which a token runs two).  `--workload tutelix`: the Tutelix decoder (windowed
 attention whose values are its keys, attention through latents, a gated delta-rule recurrence) beside Vononex, the
 closest design here (paged attention beside a recurrence with a state of fixed size), at the same widths.
+`--workload vozirax`: the Vozirax decoder (a selective state-space recurrence, differential attention with a layer that
+reads another's keys and values, gated and routed feed-forwards side by side with the mixers) beside Tutelix.
 """
 from __future__ import annotations
 
@@ -438,6 +440,32 @@ def tutelix_config(size):
             "layers": [{"type": t, "mixer": mixers[t], "mlp": {"kind": "dense", "ff": z["ff"]}} for t in TUTELIX_LAYERS]}
 
 
+# ---- the Vozirax decoder beside Tutelix at equal sizes -----------------------------------------------
+# State-space layers of twice the width inside (heads of 64 values over a state of 128, B and C shared by all heads, four
+# taps, the norm in eight parts); differential attention with two maps of 64 dims a head over values of 128 (a cache row of
+# 128, as in the decoder beside it) on a quarter as many key/value heads, the third layer reading the second one's keys and
+# values; a gated feed-forward of 8/3 the width, or eight experts without gates of which a token runs two (four groups,
+# three kept), whose inner width gives a token the dense layer's parameters.
+VOZIRAX_SIZES = {"2048": dict(width=2048, heads=16, kv=4, ff=5504, expert_ff=4096),
+                 "4096": dict(width=4096, heads=32, kv=8, ff=11008, expert_ff=8192)}
+VOZIRAX_LAYERS = ("mamba2 + dense", "attention + moe", "attention reads 1 + dense", "mamba2 + moe")
+
+
+def vozirax_config(size):
+    z = VOZIRAX_SIZES[size]
+    W = z["width"]
+    ssm = {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 8, "conv": 4}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.6,
+           "q_temp": {"coef": 0.5, "every": 128}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+           "router": {"experts": 8, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 3}}}
+    layers = [{"type": "mamba2", "mixer": ssm, "mlp": dense}, {"type": "attention", "mixer": att, "mlp": moe},
+              {"type": "attention", "mixer": dict(att, kv_from=1), "mlp": dense}, {"type": "mamba2", "mixer": ssm, "mlp": moe}]
+    return {"architecture": "Vozirax", "vocab": 50272, "width": W, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "init_std": 0.02,
+            "max_positions": CONTEXT, "layers": layers}
+
+
 def build_vononex(size, dtype="bfloat16", config=None):
     import torch
     from transformers_neuronx_b200.config import config_from_dict
@@ -515,6 +543,15 @@ def workload_tutelix(steps, warmup, sizes=None, only=None, batch=8):
                             layers=TUTELIX_LAYERS, config=tutelix_config, beside="vononex")
 
 
+def workload_vozirax(steps, warmup, sizes=None, only=None, batch=8):
+    """workload_vononex for the Vozirax decoder, with Tutelix at the same width beside it."""
+    return workload_vononex(steps, warmup, sizes or ["2048", "4096"], only, batch, design="vozirax", table=VOZIRAX_SIZES,
+                            layers=VOZIRAX_LAYERS, config=vozirax_config, beside="tutelix")
+
+
+BESIDE_CONFIGS = {"vononex": None, "tutelix": tutelix_config}       # the designs that can stand beside another (None: Vononex's own)
+
+
 def workload_vononex(steps, warmup, sizes=None, only=None, batch=8, design="vononex", table=None, layers=None, config=None,
                      beside="opt"):
     """Prefill (one 2,048-token prompt) and decode (batch 1, 8, 64, contexts ending at 2,048) of a four-layer
@@ -540,10 +577,10 @@ def workload_vononex(steps, warmup, sizes=None, only=None, batch=8, design="vono
             if which == design:
                 model, cfg = build_vononex(size, config=config)
                 tables = cfg.vocab * cfg.width * 2                    # the embedding table: rows of the batch only
-            elif which == "vononex":
-                if str(z["width"]) in {k.split("_")[1] for k in rows if k.startswith("vononex_")}:
+            elif which in BESIDE_CONFIGS:
+                if str(z["width"]) in {k.split("_")[1] for k in rows if k.startswith(which + "_")}:
                     continue                                          # this width stands in the table already
-                model, cfg = build_vononex(str(z["width"]))
+                model, cfg = build_vononex(str(z["width"]), config=BESIDE_CONFIGS[which])
                 tables, size = cfg.vocab * cfg.width * 2, str(z["width"])
             else:
                 model, cfg = build(len(layers), dtype="bfloat16", base=opt_cfg)
@@ -573,6 +610,8 @@ def extra_workload(name, steps, warmup, sizes=None, only=None, batch=8):
         res = workload_pifelix(steps, warmup, sizes, only, batch)
     elif name == "tutelix":
         res = workload_tutelix(steps, warmup, sizes, only, batch)
+    elif name == "vozirax":
+        res = workload_vozirax(steps, warmup, sizes, only, batch)
     elif name == "family":
         res = workload_family(steps, warmup, sizes)
     elif name == "sweep":
@@ -608,10 +647,10 @@ def main():
     ap.add_argument("--skip-large", action="store_true", help="leave out the OPT-13B and OPT-30B workloads")
     ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
                     help="the serving type (float16 is what OPT checkpoints are stored in)")
-    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep", "vononex", "pifelix", "tutelix"],
+    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep", "vononex", "pifelix", "tutelix", "vozirax"],
                     help="run one of the further workloads instead of the default line")
     ap.add_argument("--sizes", default=None, help="for --workload family: comma-separated sizes (default: all of 125m .. 66b); for --workload vononex: "
-                    "widths (2048, 4096); for --workload tutelix: 2048, 4096, 2048wide")
+                    "widths (2048, 4096); for --workload tutelix: 2048, 4096, 2048wide; for --workload vozirax: 2048, 4096")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run just this part and print its time (for profiling a small case)")
     a = ap.parse_args()

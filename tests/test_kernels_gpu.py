@@ -471,12 +471,14 @@ def test_attention_decode_appends_the_new_token(n_heads, n_kv, d, n_splits, warp
     assert bool(torch.isnan(case.cache.float()[~written]).all()), "nothing else was written"
 
 
-@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 128), (8, 2, 64), (8, 2, 128), (4, 1, 80), (2, 1, 112), (4, 2, 96), (6, 2, 64)])
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 128), (8, 2, 64), (8, 2, 128), (4, 1, 80), (2, 1, 112), (4, 2, 96), (6, 2, 64),
+                                            (16, 2, 64), (8, 1, 128), (12, 2, 64)])
 @pytest.mark.parametrize("window", [None, 50])
 @pytest.mark.parametrize("n_splits,warps", [(None, None), (1, 4), (3, 4), (1, 8), (5, 8), (3, 16), (44, 4)])
 def test_attention_decode_with_a_key_value_heads_query_heads_in_one_block(n_heads, n_kv, d, window, n_splits, warps):
-    """Grouped key/value heads: a block takes the 2 or 4 query heads of a key/value head and reads its pages once;
-    sizes the grouped form does not take (3 query heads a key/value head, head size 96) run one block a head.  With and
+    """Grouped key/value heads: a block takes 2 or 4 query heads of a key/value head and reads its pages once for them
+    (with 8 or 6 query heads a key/value head, two or three blocks share it); sizes the grouped form does not take
+    (3 query heads a key/value head, head size 96) run one block a head.  With and
     without the cache append, twice (the split counters must be back at zero)."""
     lens = [(0, 1), (15, 1), (16, 1), (17, 1), (255, 1), (256, 1), (700, 1), (63, 1)]
     case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=d + 5)

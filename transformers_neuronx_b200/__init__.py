@@ -8,7 +8,7 @@ from .config.generation_config import (BlkSparseAttnConfig, ContinuousBatchingCo
                                        SlidingWindowAttnConfig, SparseAttnConfig)      # as `from transformers_neuronx import ...`
 
 _LAZY = {"OPTForSampling": ".opt.model", "OPTForGreedySearch": ".opt.model", "VononexForSampling": ".vononex.model", "PifelixForSampling": ".pifelix.model",
-         "TutelixForSampling": ".tutelix.model",
+         "TutelixForSampling": ".tutelix.model", "VoziraxForSampling": ".vozirax.model",
          "NeuronAutoModelForCausalLM": ".modeling_auto", "HuggingFaceGenerationModelAdapter": ".generation_utils"}
 
 

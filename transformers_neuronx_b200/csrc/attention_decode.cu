@@ -425,12 +425,15 @@ int launch_decode(int warps, int rep, dim3 grid, cudaStream_t stream, const Deco
     return tnx_launch_in_order(attention_decode_kernel<LPK, E, 4, 1>, grid, dim3(4 * 32), 0, stream, p);
 }
 
-// How many query heads a block takes for these sizes: the query heads per key/value head where that is 2 or 4 and the
-// head size is one whose 8-dim pieces fill 8 or 16 lanes a key (64, 80 .. 128); 1 otherwise (one block per query head).
+// How many query heads a block takes for these sizes: 4 where the query heads per key/value head are a multiple of 4
+// (with 8 of them, the two maps of differential attention on 4 heads a key/value head, two blocks share a key/value
+// head), 2 where they are a multiple of 2, and the head size is one whose 8-dim pieces fill 8 or 16 lanes a key (64,
+// 80 .. 128); 1 otherwise (one block per query head).  A block's heads are neighbours, so they share their key/value head.
 int gqa_rep(int n_heads, int n_kv_heads, int head_dim) {
     const int group = n_heads / n_kv_heads, chunks = head_dim / 8;
     const bool lanes_8_or_16 = chunks == 5 || chunks == 7 || chunks == 8 || (chunks > 8 && chunks <= 16 && chunks != 12);
-    return ((group == 2 || group == 4) && lanes_8_or_16) ? group : 1;
+    const int rep = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+    return lanes_8_or_16 ? rep : 1;
 }
 
 }  // namespace

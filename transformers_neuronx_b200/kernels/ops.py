@@ -653,7 +653,7 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     # (a layer's step 1.58 against 1.77 ms at 64 rows, 2.44 against 2.78 at 128) and loses below (1.34 against 1.18 at 32:
     # its blocks are a quarter as many, one an SM), so it runs once the (row, key/value head) pairs are three an SM.
     heads_per_block = lib.tnx_attention_decode_heads_per_block(c_int(n_heads), c_int(n_kv), c_int(d))
-    if grouped is False or (grouped is None and R * n_kv < 3 * st["sms"]):
+    if grouped is False or (grouped is None and R * n_heads // heads_per_block < 3 * st["sms"]):
         heads_per_block = 1
     if n_splits is None:
         warps, n_splits = decode_attention_plan(R * n_heads // heads_per_block, st["sms"], d, max_pages)

@@ -22,7 +22,8 @@ _NAMES = ("embed", "gather_rows", "patch_tokens", "layer_norm", "pick_rows", "ge
           "attention_simt", "attention_decode", "attention_prefill", "attention_prefill_tc", "sample", "sample_packed",
           "rms_norm", "rotary_qkv_prep", "rotary_unrotate", "retention_prep", "retention_scan", "retention_decode", "headwise_gated_rms_norm",
           "mingru_scan", "gated_activation", "rms_norm_add", "conv_qkv_prep", "moe_route", "moe_experts", "moe_sort_rows",
-          "gemm_tc_grouped", "moe_activation", "moe_combine", "latent_prep", "headwise_product", "delta_prep", "delta_scan")
+          "gemm_tc_grouped", "moe_activation", "moe_combine", "latent_prep", "headwise_product", "delta_prep", "delta_scan",
+          "ssd_prep", "ssd_gate_norm", "diff_qkv_prep", "diff_combine", "rms_norm_pair", "scaled_residual_add")
 
 
 class KernelProfile:
