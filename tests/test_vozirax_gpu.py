@@ -83,7 +83,16 @@ def test_two_norms_of_one_row_and_two_scaled_results_into_the_stream(W, dtype):
     ops.scaled_residual_add(xs, a.to(DEV), w1.to(DEV), b.to(DEV), w2.to(DEV))
     _close(xs, x.double() + a.double() * w1.double() + b.double() * w2.double(), 1e-6)
     ops.scaled_residual_add(xs, a.to(DEV))
-    _close(xs, x.double() + a.double() * (w1.double() + 1.0) + b.double() * w2.double(), 1e-6)
+    new = x.double() + a.double() * (w1.double() + 1.0) + b.double() * w2.double()
+    _close(xs, new, 1e-6)
+    # the kernel that closes a layer also forms the two norms of the layer that follows
+    ops.scaled_residual_add(xs, b.to(DEV), w2.to(DEV), a.to(DEV), None, then=(w2.to(DEV), 1.0, 1e-3, o1, w1.to(DEV), 0.0, 1e-5, o2))
+    new = new + b.double() * w2.double() + a.double()
+    _close(xs, new, 1e-6)
+    _close(o1, ZP.rms(new, 1e-3, 1.0 + w2.double()), tol)
+    _close(o2, ZP.rms(new, 1e-5, w1.double()), tol)
+    ops.scaled_residual_add(xs, a.to(DEV), then=(None, 0.0, 1e-5, only, None, 0.0, 0.0, None))
+    _close(only, ZP.rms(new + a.double(), 1e-5), tol)
 
 
 def _plain_maps(u, H, G, dk, dv, qn, kn, eps, temp, positions):

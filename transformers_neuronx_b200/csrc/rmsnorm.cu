@@ -73,16 +73,34 @@ __global__ void rms_norm_pair_kernel(const float* __restrict__ x, const float* _
 }
 
 // x <- x + s1 * a (+ s2 * b): two sublayers' results, each multiplied channel by channel by a learned scale, enter
-// the 32-bit stream in one pass (s1, s2 absent: 1; b absent: one sublayer).
+// the 32-bit stream in one pass (s1, s2 absent: 1; b absent: one sublayer).  With out1 the new row's norms for the two
+// sublayers of the layer that follows are formed in the same kernel (the row stays in shared memory):
+// out_i = x / sqrt(mean(x^2) + eps_i) * (w_i + off_i), out2 optional.
+template <typename TA>
 __global__ void scaled_residual_add_kernel(float* x, const float* __restrict__ a, const float* __restrict__ s1,
-                                           const float* __restrict__ b, const float* __restrict__ s2, int H) {
+                                           const float* __restrict__ b, const float* __restrict__ s2, int H,
+                                           const float* __restrict__ w1, float off1, float eps1, TA* __restrict__ out1,
+                                           const float* __restrict__ w2, float off2, float eps2, TA* __restrict__ out2) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const size_t src = (size_t)blockIdx.x * H;
+    float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float d = a[src + c] * (s1 ? s1[c] : 1.f);
         if (b) d = fmaf(b[src + c], s2 ? s2[c] : 1.f, d);
-        x[src + c] += d;
+        const float v = x[src + c] + d;
+        x[src + c] = v;
+        if (out1) { row[c] = v; ss = fmaf(v, v, ss); }
+    }
+    if (!out1) return;
+    const float ms = block_sum(ss, scratch) / (float)H;
+    const float r1 = 1.0f / sqrtf(ms + eps1), r2 = 1.0f / sqrtf(ms + eps2);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {           // a thread reads back what it wrote itself
+        const float v = row[c];
+        out1[src + c] = from_float<TA>(v * r1 * (w1 ? w1[c] + off1 : 1.f));
+        if (out2) out2[src + c] = from_float<TA>(v * r2 * (w2 ? w2[c] + off2 : 1.f));
     }
 }
 
@@ -221,11 +239,24 @@ TNX_EXPORT int tnx_rms_norm_pair(const float* x, const float* w1, float off1, fl
 }
 
 TNX_EXPORT int tnx_scaled_residual_add(float* x, const float* a, const float* s1, const float* b, const float* s2,
-                                       int n_rows, int H, cudaStream_t stream) {
+                                       int n_rows, int H, const float* w1, float off1, float eps1, void* out1,
+                                       const float* w2, float off2, float eps2, void* out2, int act_h16,
+                                       cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (H <= 0 || !x || !a) return TNX_ERR_BAD_ARG;
+    if (H <= 0 || !x || !a || (out2 && !out1)) return TNX_ERR_BAD_ARG;
+    const size_t smem = out1 ? (size_t)H * sizeof(float) : 0;
+    if (smem > 200 * 1024) return TNX_ERR_UNSUPPORTED;
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
-    return tnx_launch_ex(1, scaled_residual_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, a, s1, b, s2, H);
+    if (act_h16) {
+        if (smem + 1024 > 48 * 1024)
+            cudaFuncSetAttribute(scaled_residual_add_kernel<h16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tnx_launch_ex(1, scaled_residual_add_kernel<h16>, dim3(n_rows), dim3(threads), smem, stream, x, a, s1, b, s2, H,
+                             w1, off1, eps1, (h16*)out1, w2, off2, eps2, (h16*)out2);
+    }
+    if (smem + 1024 > 48 * 1024)
+        cudaFuncSetAttribute(scaled_residual_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return tnx_launch_ex(1, scaled_residual_add_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, a, s1, b, s2, H,
+                         w1, off1, eps1, (float*)out1, w2, off2, eps2, (float*)out2);
 }
 
 TNX_EXPORT int tnx_rms_norm(const float* x, float x_scale, const float* delta, const int* rows, const float* w,

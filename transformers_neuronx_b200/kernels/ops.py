@@ -653,9 +653,25 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     # (a layer's step 1.58 against 1.77 ms at 64 rows, 2.44 against 2.78 at 128) and loses below (1.34 against 1.18 at 32:
     # its blocks are a quarter as many, one an SM), so it runs once the (row, key/value head) pairs are three an SM.
     heads_per_block = lib.tnx_attention_decode_heads_per_block(c_int(n_heads), c_int(n_kv), c_int(d))
-    if grouped is False or (grouped is None and R * n_heads // heads_per_block < 3 * st["sms"]):
+    # Measured again with 8 query heads a key/value head (the two maps of differential attention; 64 heads on 8, contexts
+    # of 2,048): between two thirds of a block and three blocks an SM the grouped form wins as well when its blocks are
+    # four warps and the context is split so that about two blocks an SM run (8 rows: 75 us with two splits against 93
+    # with a block a head; 16 rows: 123 against 153; the plan drawn for one head a block gave 107 and 206 there).
+    few_grouped = False
+    if heads_per_block > 1 and grouped is None:
+        blocks = R * n_heads // heads_per_block
+        if blocks < 3 * st["sms"]:
+            few_grouped = 3 * blocks >= 2 * st["sms"] and n_splits is None
+            if not few_grouped:
+                heads_per_block = 1
+    elif grouped is False:
         heads_per_block = 1
-    if n_splits is None:
+    if few_grouped:
+        warps = 4
+        n_splits = max(1, min(max_pages // 8, (2 * st["sms"] + blocks // 2) // blocks))
+        pps = -(-max_pages // n_splits)
+        pps = -(-pps // warps) * warps
+    elif n_splits is None:
         warps, n_splits = decode_attention_plan(R * n_heads // heads_per_block, st["sms"], d, max_pages)
         if heads_per_block > 1 and warps == 16:
             warps = 8                                           # their accumulators leave no registers for sixteen warps
@@ -839,9 +855,13 @@ def rms_norm_pair(x, weight1, offset1, eps1, out1, weight2=None, offset2=0.0, ep
            "rms_norm_pair")
 
 
-def scaled_residual_add(x, a, scale_a=None, b=None, scale_b=None):
-    """x += scale_a * a (+ scale_b * b), all 32-bit; the scales are vectors over the hidden axis (None: 1)."""
-    lib = _build.load("rmsnorm")
+def scaled_residual_add(x, a, scale_a=None, b=None, scale_b=None, then=None):
+    """x += scale_a * a (+ scale_b * b), all 32-bit; the scales are vectors over the hidden axis (None: 1).
+    then = (weight1, offset1, eps1, out1, weight2, offset2, eps2, out2): the new rows' two RMS norms (as rms_norm_pair
+    forms them; out2 None: one) are written in the same kernel: the inputs of the sublayers of the layer that follows."""
+    out1 = then[3] if then is not None else None
+    out2 = then[7] if then is not None else None
+    lib = _lib("rmsnorm", out1, out2)
     _need(x, "x", torch.float32, 2)
     N, H = x.shape
     for t, nm in ((a, "a"), (b, "b")):
@@ -850,8 +870,19 @@ def scaled_residual_add(x, a, scale_a=None, b=None, scale_b=None):
             if tuple(t.shape) != (N, H):
                 raise KernelError(f"{nm} must have the shape of x")
     _f32_vec(scale_a, "scale_a", H); _f32_vec(scale_b, "scale_b", H)
-    _check(lib.tnx_scaled_residual_add(_p(x), _p(a), _p(scale_a), _p(b), _p(scale_b), c_int(N), c_int(H), _stream()),
-           "scaled_residual_add")
+    w1 = w2 = None
+    off1 = eps1 = off2 = eps2 = 0.0
+    if then is not None:
+        w1, off1, eps1, _, w2, off2, eps2, _ = then
+        _f32_vec(w1, "weight1", H); _f32_vec(w2, "weight2", H)
+        for t, nm in ((out1, "out1"), (out2, "out2")):
+            if t is not None:
+                _need(t, nm, out1.dtype if nm == "out2" else _FLOATS, 2)
+                if tuple(t.shape) != (N, H):
+                    raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{N}, {H}]")
+    _check(lib.tnx_scaled_residual_add(_p(x), _p(a), _p(scale_a), _p(b), _p(scale_b), c_int(N), c_int(H), _p(w1),
+                                       c_float(off1), c_float(eps1), _p(out1), _p(w2), c_float(off2), c_float(eps2), _p(out2),
+                                       c_int(_is_h16(out1) if out1 is not None else 0), _stream()), "scaled_residual_add")
 
 
 def rms_norm_add(x, add_scale, delta, weight, eps, out_f32=None, out_act=None, weight_offset=0.0, then=None):

@@ -123,6 +123,7 @@ class DecoderModel:
         self.embedding.forward(ctx, x, x_act if (first is not None and first.needs_act_input) else None)
         act_current = first is not None and first.needs_act_input
         taps = self._taps
+        ctx.handed_on = None
         if taps is not None:
             taps.clear()
             taps["embedding"] = x.clone()
@@ -131,6 +132,8 @@ class DecoderModel:
             if block.needs_act_input and not act_current:
                 ops.pick_rows(x, None, out_act=x_act)
             ctx.cache_id = e.cache
+            ctx.entry_index = i
+            ctx.next_block = self.blocks[self.spec.schedule[i + 1].layer] if i + 1 < len(self.spec.schedule) else None
             ctx.begin_entry()
             block.forward(ctx, x, x_act)
             act_current = block.keeps_act_current

@@ -59,6 +59,10 @@ class StepContext:
         self.max_decode_ctx = 0
         self._scratch_pool = {}
         self._scratch_used = {}
+        self._carry_pool = {}
+        self.entry_index = -1                 # which schedule entry runs (set by the model)
+        self.next_block = None                # the block of the entry after it, or None
+        self.handed_on = None                 # (entry index, block, tensors...): inputs a block prepared for the next one
 
     def empty(self, rows, cols, dtype=None) -> torch.Tensor:
         return torch.empty((rows, cols), dtype=dtype or self.act_dtype, device=self.device)
@@ -74,6 +78,15 @@ class StepContext:
         if i == len(have):
             have.append(torch.empty((rows, cols), dtype=key[2], device=self.device))
         return have[i]
+
+    def carry(self, which, rows, cols, dtype=None) -> torch.Tensor:
+        """A buffer that outlives the schedule entry that fills it: a block that prepares the next block's inputs in its
+        own last kernel writes them here (`which`: any hashable name; entries alternate between two sets, so what the
+        running entry reads is not what it writes for the next)."""
+        key = (which, rows, cols, dtype or self.act_dtype)
+        if key not in self._carry_pool:
+            self._carry_pool[key] = torch.empty((rows, cols), dtype=key[3], device=self.device)
+        return self._carry_pool[key]
 
     def begin_entry(self) -> None:
         """Called before each schedule entry runs: the scratch buffers of the entry before are free."""

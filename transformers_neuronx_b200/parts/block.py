@@ -216,18 +216,32 @@ class ParallelResidualBlock(ScaledPostNormBlock):
 
     def forward(self, ctx, x, x_act):
         N, W = x.shape
-        h1 = ctx.scratch(N, W)
         two = self.feed_forward is not None
-        h2 = ctx.scratch(N, W) if two else None
-        self.norm1.forward_pair(ctx, x, h1, self.norm2 if two else None, h2)
+        handed, ctx.handed_on = getattr(ctx, "handed_on", None), None
+        if handed is not None and handed[0] == ctx.entry_index and handed[1] is self:
+            h1, h2 = handed[2], handed[3]          # the block before formed them in the kernel that closed its layer
+        else:
+            h1 = ctx.scratch(N, W)
+            h2 = ctx.scratch(N, W) if two else None
+            self.norm1.forward_pair(ctx, x, h1, self.norm2 if two else None, h2)
         a = ctx.scratch(N, W, x.dtype)
         self._run(ctx, self.mixer, h1, a)
         b = None
         if two:
             b = ctx.scratch(N, W, x.dtype)
             self._run(ctx, self.feed_forward, h2, b)
+        # the layer that follows, if it is of this kind, gets its two norms from the kernel that closes this one
+        nxt, then = getattr(ctx, "next_block", None), None
+        if isinstance(nxt, ParallelResidualBlock):
+            par = (ctx.entry_index + 1) & 1
+            n1, n2 = nxt.norm1, (nxt.norm2 if nxt.feed_forward is not None else None)
+            o1 = ctx.carry(("pair", par, 0), N, W)
+            o2 = ctx.carry(("pair", par, 1), N, W) if n2 is not None else None
+            then = (n1.weight, n1.spec.weight_offset, n1.spec.eps, o1, n2.weight if n2 is not None else None,
+                    n2.spec.weight_offset if n2 is not None else 0.0, n2.spec.eps if n2 is not None else 0.0, o2)
+            ctx.handed_on = (ctx.entry_index + 1, nxt, o1, o2)
         ops.scaled_residual_add(x, a, self.scale1.weight if self.scale1 else None, b,
-                                self.scale2.weight if self.scale2 else None)
+                                self.scale2.weight if self.scale2 else None, then=then)
 
 
 register_block("pre_norm", PreNormBlock)
