@@ -91,7 +91,7 @@ __host__ __device__ __forceinline__ int token_gate_floats(int stage_tokens) { re
 // A stage holds q [ST][DKP], k [ST][DKP] (columns from k_dim on stay zero) and v [ST][C], ST = stage_tokens: 32 for
 // portions of prompts, as few as one for a step of single tokens (less shared memory, more blocks an SM).
 template <typename T, int KPT, int R, bool VEC, bool VASYNC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(16 * R < 128 ? 128 : 16 * R)
 retention_scan_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v, int v_ld,
                       const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ q_start,
                       const int* __restrict__ q_len, const int* __restrict__ state_slots, float* __restrict__ out,
@@ -562,6 +562,8 @@ TNX_EXPORT int tnx_retention_prep(const void* proj, int ld, int q_off, int k_off
 // idle lanes), so that even one request of a few heads spreads over many SMs and every block is whole warps.
 TNX_EXPORT int tnx_retention_scan_columns(int dv) { return dv >= 16 ? 16 : 8; }
 
+static int g_force_lanes = 0, g_force_stage = 0;
+
 template <typename T>
 static int retention_scan_launch(const float* qr, const float* kr, const T* v, int v_ld, const float* decay, float* state,
                                  const int* q_start, const int* q_len, const int* state_slots, float* out, int n_requests,
@@ -620,10 +622,19 @@ static int retention_scan_launch(const float* qr, const float* kr, const T* v, i
     if (dk <= 16) SCAN(4, 4);
     if (dk <= 32) SCAN(4, 8);
     if (dk <= 64) SCAN(8, 8);
-    if (dk <= 128) SCAN(16, 8);
+    if (dk <= 128) { if (g_force_lanes == 16) SCAN(8, 16); SCAN(16, 8); }
     if (dk <= 256) SCAN(32, 8);
     return TNX_ERR_UNSUPPORTED;
 #undef SCAN
+}
+
+// A test and measurement hook: the lanes a column's rows are spread over (0: the kernel's own choice; 16 for key sizes
+// of 65 to 128) and the most tokens of a stage (0: SCAN_TOKENS_MOST).
+TNX_EXPORT int tnx_retention_scan_force(int lanes, int stage_tokens) {
+    if ((lanes != 0 && lanes != 16) || stage_tokens < 0 || stage_tokens > SCAN_TOKENS_MOST) return TNX_ERR_BAD_ARG;
+    g_force_lanes = lanes;
+    g_force_stage = stage_tokens;
+    return 0;
 }
 
 TNX_EXPORT int tnx_retention_scan(const float* qr, const float* kr, const void* v, int v_ld, const float* decay,
@@ -638,7 +649,19 @@ TNX_EXPORT int tnx_retention_scan(const float* qr, const float* kr, const void* 
     if (qk_heads <= 0 || H % qk_heads || (!decay && !decay_tok)) return TNX_ERR_BAD_ARG;
     const TokenGates tg{decay_tok, kscale_tok, qk_heads};
     int stage_tokens = 1;
-    while (stage_tokens < most_tokens && stage_tokens < SCAN_TOKENS_MOST) stage_tokens *= 2;
+    int stage_most = g_force_stage ? g_force_stage : SCAN_TOKENS_MOST;
+    if (!g_force_stage && dk > 64) {
+        // Stages of 32 tokens of 128-row keys and queries take 86 KB, so an SM holds two blocks.  With more blocks than
+        // that, smaller stages (more blocks at once, a rendezvous more often) are faster.  Measured at 128 rows and 64
+        // columns a head, 2,048 tokens: 256 blocks 471 / 499 / 564 us with 32 / 16 / 8 tokens a stage, 512 blocks 920 / 793 /
+        // 855, 2,048 blocks (eight requests of 256 tokens) 424 / 368 / 354.
+        static int sms = 0;
+        if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms <= 0) sms = 1; }
+        const int C = tnx_retention_scan_columns(dv);
+        const long long blocks = (long long)((dv + C - 1) / C) * H * n_requests;
+        stage_most = blocks <= 2LL * sms ? 32 : (blocks <= 8LL * sms ? 16 : 8);
+    }
+    while (stage_tokens < most_tokens && stage_tokens < stage_most) stage_tokens *= 2;
     if (v_h16)
         return retention_scan_launch<h16>(qr, kr, (const h16*)v, v_ld, decay, state, q_start, q_len, state_slots, out,
                                           n_requests, H, dk, dv, stage_tokens, tg, stream);
