@@ -83,7 +83,7 @@ def test_pages_and_state_of_every_layer():
     (lambda d: d["layers"][0]["mlp"]["router"]["groups"].update(count=4), "equal groups"),
     (lambda d: d["layers"][0]["mlp"]["router"]["groups"].update(keep=1), "fewer than"),
     (lambda d: d["layers"][0]["mlp"].update(kind="switch"), "kind"),
-    (lambda d: d.pop("logit_scale"), "logit_scale"),
+    (lambda d: d.update(logit_scale="big"), "logit_scale"),
     (lambda d: d["norm"].update(eps=0.0), "eps")])
 def test_a_configuration_that_cannot_be_run_is_refused_by_name(edit, word):
     from transformers_neuronx_b200.config import ConfigError, config_from_dict
@@ -91,6 +91,18 @@ def test_a_configuration_that_cannot_be_run_is_refused_by_name(edit, word):
     edit(d)
     with pytest.raises(ConfigError, match=word):
         config_from_dict(d)
+
+
+def test_a_mechanism_whose_key_is_absent_is_not_there():
+    d = copy.deepcopy(CONFIG_A)
+    d.pop("logit_scale")
+    d["layers"][3]["mixer"].pop("groups"); d["layers"][3]["mixer"].pop("norm_groups")
+    d["layers"][4]["mixer"].pop("kv_heads")
+    d["layers"][3]["mlp"]["router"].pop("scale")
+    _, cfg, spec = _spec(d)
+    assert spec.head.logit_scale == 1.0 and spec.layers[3].mixer.groups == 1 and spec.layers[3].mixer.norm_groups == 1
+    assert spec.layers[4].mixer.n_kv_heads == 3 and spec.layers[3].feed_forward.weight_scale == 1.0
+    assert spec.layers[1].feed_forward is None and spec.layers[4].mixer.temp_every == 0 and spec.layers[3].feed_forward.n_groups == 1
 
 
 def test_sizes_the_kernels_do_not_take_are_refused_when_the_model_is_built():

@@ -243,6 +243,33 @@ def test_the_state_space_recurrence_across_cuts_and_slots(H, P, G, N, taps, dtyp
     _close(got[0], plain(seqs[2]), tol)
 
 
+@pytest.mark.parametrize("lanes, stage", [(0, 0), (0, 8), (0, 2), (16, 0), (16, 4)])
+def test_the_scan_does_not_depend_on_how_its_tokens_are_staged(lanes, stage):
+    """Stages of 32, 8 or 2 tokens and a column's rows over 8 or 16 lanes (the kernel chooses by the number of blocks; a
+    hook imposes them): the state is the same bit for bit, the outputs to the order of a sum."""
+    from transformers_neuronx_b200.kernels import ops
+    g = torch.Generator().manual_seed(9)
+    H, P, G, N, T = 4, 32, 2, 128, 75
+    c, b = torch.randn(T, G * N, generator=g).to(DEV), torch.randn(T, G * N, generator=g).to(DEV)
+    x, dt = torch.randn(T, H * P, generator=g).to(DEV), torch.rand(T, H, generator=g).to(DEV)
+    dec = (torch.rand(T, H, generator=g) * 0.3 + 0.7).to(DEV)
+    ctx = _ctx([(1, 0, T)], pad_rows=0)
+
+    def run():
+        state, y = torch.zeros(2, H, P, N, device=DEV), torch.empty(T, H * P, device=DEV)
+        ops.retention_scan(c, b, x, None, state, ctx.q_start, ctx.q_len, ctx.state_slots, y, H, N, P, most_tokens=T,
+                           decay_tok=dec, kscale_tok=dt, qk_heads=G)
+        return state, y
+    want_state, want_y = run()
+    ops.retention_scan_force(lanes, stage)
+    try:
+        state, y = run()
+    finally:
+        ops.retention_scan_force(0, 0)
+    assert torch.equal(state, want_state)
+    _close(y, want_y.cpu(), 0.0 if lanes == 0 else 2e-6)
+
+
 @pytest.mark.parametrize("inner, P, parts, dtype", [(60, 10, 3, torch.float32), (256, 64, 1, torch.bfloat16), (256, 32, 8, torch.float32),
                                                     (50, 50, 5, torch.float32)])
 def test_the_gate_comes_before_the_norm_in_parts(inner, P, parts, dtype):

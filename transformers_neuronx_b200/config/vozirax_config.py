@@ -10,7 +10,9 @@ A layer's `type` names its mixer:
 A layer's `mlp` is {"kind": "dense", "ff": F}, or {"kind": "moe", "expert": {"ff": F}, "router": {"experts": E, "top": k,
 "scale": s, optionally "groups": {"count": n, "keep": m}}}, or null.  Every layer carries its own sizes, so layers of
 one model may differ.  Nothing has a default but `init_std` (the spread of random weights, used only when a folder is
-written from a seed) and `max_positions` (the longest request the engine admits; the design itself has no limit).
+written from a seed) and `max_positions` (the longest request the engine admits; the design itself has no limit); a
+mechanism whose key is absent is not there (`logit_scale` and a router's `scale`: 1; `groups` and `norm_groups` of a
+state-space layer: 1; `kv_heads`: as many as heads; `q_temp`, a router's `groups`, `kv_from`: none).
 """
 from __future__ import annotations
 
@@ -54,7 +56,8 @@ def _check_mlp(mlp, where):
     E, top = _pos_int(r, "experts", rw), _pos_int(r, "top", rw)
     if top > E:
         raise ConfigError(f"{rw}: {top} of {E} experts is not a choice")
-    _number(r, "scale", rw)
+    if r.get("scale") is not None:
+        _number(r, "scale", rw)
     g = r.get("groups")
     if g is not None:
         if not isinstance(g, dict):
@@ -78,6 +81,8 @@ def _check_layer(i: int, layer: Dict[str, Any], layers) -> None:
         raise ConfigError(f"{where}: key 'mixer' must hold the mixer's sizes")
     mw = where + ".mixer"
     if layer["type"] == "mamba2":
+        m.setdefault("groups", 1)             # what the file does not mention is not there: one group of B and C,
+        m.setdefault("norm_groups", 1)        # a norm over the whole inner width
         for k in ("heads", "vdim", "state", "groups", "norm_groups", "conv"):
             _pos_int(m, k, mw)
         if m["heads"] % m["groups"]:
@@ -85,6 +90,8 @@ def _check_layer(i: int, layer: Dict[str, Any], layers) -> None:
         if (m["heads"] * m["vdim"]) % m["norm_groups"]:
             raise ConfigError(f"{mw}: {m['heads'] * m['vdim']} inner channels do not form {m['norm_groups']} equal parts")
     else:
+        if isinstance(m.get("heads"), int):
+            m.setdefault("kv_heads", m["heads"])
         for k in ("heads", "kv_heads", "dim", "vdim"):
             _pos_int(m, k, mw)
         if m["heads"] % m["kv_heads"]:
@@ -154,7 +161,7 @@ class VoziraxConfig:
 
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "VoziraxConfig":
-        missing = [k for k in ("vocab", "width", "layers", "norm", "logit_scale") if k not in d]
+        missing = [k for k in ("vocab", "width", "layers", "norm") if k not in d]
         if missing:
             raise ConfigError("config.json lacks required key(s): " + ", ".join(missing))
         if not isinstance(d["norm"], dict) or "eps" not in d["norm"]:
@@ -162,7 +169,8 @@ class VoziraxConfig:
         if not isinstance(d["layers"], list):
             raise ConfigError("config key 'layers' must be a list")
         kw = dict(vocab=d["vocab"], width=d["width"], layers=tuple(copy.deepcopy(l) for l in d["layers"]),
-                  norm_eps=float(d["norm"]["eps"]), logit_scale=_number(d, "logit_scale", "config"))
+                  norm_eps=float(d["norm"]["eps"]),
+                  logit_scale=_number(d, "logit_scale", "config") if d.get("logit_scale") is not None else 1.0)
         for k in ("init_std", "max_positions"):
             if k in d:
                 kw[k] = d[k]

@@ -1281,6 +1281,15 @@ def retention_decode(proj, q_off, k_off, v_off, g_off, positions, inv_freq, rot_
     return True
 
 
+def retention_scan_force(lanes=0, stage_tokens=0, dtype=None) -> None:
+    """A test and measurement hook: the lanes a column's rows are spread over (0: the kernel's own choice; 16 for key
+    sizes of 65 to 128) and the most tokens of a stage (0: the kernel's own choice, which follows the number of blocks).
+    `dtype`: which flavour of the library (the 16-bit type of the values it will be given; None: bfloat16's)."""
+    lib = _build.load("retention", dtype if dtype in _H16 else None)
+    if lib.tnx_retention_scan_force(c_int(int(lanes)), c_int(int(stage_tokens))) != 0:
+        raise KernelError(f"retention_scan_force: {lanes} lanes (0 or 16) and stages of {stage_tokens} tokens (0 to 32) are not a choice")
+
+
 def headwise_gated_rms_norm(o, gate, token_request, weight, eps, out_scale, out, n_heads, v_dim, gate_activation="silu"):
     """out = o / rms(o over each head's v_dim dims) (* weight) * act(gate) * out_scale; o 32-bit [N, n_heads * v_dim],
     gate (optional) and out views in the activation type; act: silu unless named otherwise."""

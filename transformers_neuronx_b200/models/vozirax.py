@@ -71,7 +71,7 @@ def _feed_forward(p: str, W: int, mlp: dict):
         experts=tuple(ExpertSpec(None, f"{p}.e{j}.up", f"{p}.e{j}.down") for j in range(E)), scores="sigmoid",
         renormalize=True, weight_on_input=False, expert_form="relu2", correction=p + ".correction",
         n_groups=g["count"] if g else 1, keep_groups=g["keep"] if g else 1, group_top=GROUP_TOP, renorm_eps=RENORM_EPS,
-        weight_scale=float(r["scale"]))
+        weight_scale=float(r["scale"]) if r.get("scale") is not None else 1.0)
 
 
 def build_spec(cfg: VoziraxConfig) -> ModelSpec:
