@@ -445,7 +445,7 @@ def tutelix_config(size):
 # taps, the norm in eight parts); differential attention with two maps of 64 dims a head over values of 128 (a cache row of
 # 128, as in the decoder beside it) on a quarter as many key/value heads, the third layer reading the second one's keys and
 # values; a gated feed-forward of 8/3 the width, or eight experts without gates of which a token runs two (four groups,
-# three kept), whose inner width gives a token the dense layer's parameters.
+# two kept), whose inner width gives a token the dense layer's parameters.
 VOZIRAX_SIZES = {"2048": dict(width=2048, heads=16, kv=4, ff=5504, expert_ff=4096),
                  "4096": dict(width=4096, heads=32, kv=8, ff=11008, expert_ff=8192)}
 VOZIRAX_LAYERS = ("mamba2 + dense", "attention + moe", "attention reads 1 + dense", "mamba2 + moe")
@@ -455,11 +455,11 @@ def vozirax_config(size):
     z = VOZIRAX_SIZES[size]
     W = z["width"]
     ssm = {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 8, "conv": 4}
-    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.6,
-           "q_temp": {"coef": 0.5, "every": 128}}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.5,
+           "q_temp": {"coef": 0.4, "every": 256}}
     dense = {"kind": "dense", "ff": z["ff"]}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
-           "router": {"experts": 8, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 3}}}
+           "router": {"experts": 8, "top": 2, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     layers = [{"type": "mamba2", "mixer": ssm, "mlp": dense}, {"type": "attention", "mixer": att, "mlp": moe},
               {"type": "attention", "mixer": dict(att, kv_from=1), "mlp": dense}, {"type": "mamba2", "mixer": ssm, "mlp": moe}]
     return {"architecture": "Vozirax", "vocab": 50272, "width": W, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "init_std": 0.02,

@@ -169,10 +169,10 @@ def test_plain_routing_keeps_the_best_groups_and_weighs_by_the_uncorrected_score
     h = torch.eye(4, dtype=torch.float64)[:1]
     t = {"router": torch.tensor([[0.0], [-1.0], [-3.0], [2.0]], dtype=torch.float64).repeat(1, 4) * torch.eye(4, dtype=torch.float64)[0],
          "correction": torch.tensor([-0.9, -0.8, -2.0, -1.5], dtype=torch.float64)}
-    r = {"experts": 4, "top": 1, "scale": 2.5, "groups": {"count": 2, "keep": 1}}
+    r = {"experts": 4, "top": 1, "scale": 3.0, "groups": {"count": 2, "keep": 1}}
     (ids, w), = ZP.route(h, t, "", r)
     # choice scores: 0.5 - 0.9, 0.269 - 0.8, 0.047 - 2.0, 0.881 - 1.5: group sums -0.93 and -2.57
-    assert ids == [0] and abs(float(w[0]) - 2.5) < 1e-9
+    assert ids == [0] and abs(float(w[0]) - 3.0) < 1e-9
     r["groups"]["keep"] = 2
     assert ZP.route(h, t, "", r)[0][0] == [0]                            # -0.4 beats -0.62 without the groups too
     t["correction"][3] = -1.2

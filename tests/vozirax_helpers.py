@@ -57,8 +57,8 @@ CONFIG_A = {"architecture": "Vozirax", "vocab": 211, "width": 72, "norm": {"eps"
 CONFIG_B = {"architecture": "Vozirax", "vocab": 1003, "width": 256, "norm": {"eps": 1e-6}, "logit_scale": 2.0, "init_std": 0.1,
             "layers": [
                 layer("mamba2", ssm(4, 64, 128, 2, 2, 4), dense(320)),
-                layer("attention", attn(4, 2, 64, 128, 0.11, 0.6, temp=(0.5, 32)), moe(8, 2, 64, 2.5, groups=(4, 2))),
-                layer("attention", attn(4, 2, 64, 128, 0.09, 0.2, temp=(1.5, 5), kv_from=1), dense(384)),
+                layer("attention", attn(4, 2, 64, 128, 0.11, 0.55, temp=(0.4, 32)), moe(8, 2, 96, 1.5, groups=(4, 2))),
+                layer("attention", attn(4, 2, 64, 128, 0.09, 0.2, temp=(0.6, 5), kv_from=1), dense(384)),
                 layer("mamba2", ssm(8, 32, 64, 1, 8, 3), moe(4, 4, 128, 1.0)),
                 layer("attention", attn(6, 3, 32, 48, 0.15, 0.5), None)]}
 # A width and a vocabulary that are no multiples of 8 (the 16-bit engine falls back to the CUDA-core product and to scalar
